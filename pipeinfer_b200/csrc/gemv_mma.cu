@@ -111,7 +111,7 @@ __device__ __forceinline__ q4k_hdr decode_hdr(const uint4 h) {
     return r;
 }
 
-// ---- TMA bulk copy + mbarrier helpers (sm_90+ PTX; SASS: UBLKCP / SYNCS) ----------------------------------------------
+// ---- TMA bulk copy + mbarrier helpers (sm_90+ PTX) ----------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void * p) { return (uint32_t) __cvta_generic_to_shared(p); }
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");

@@ -13,6 +13,6 @@ PIB_GRAPHS=0 ncu --metrics gpu__time_duration.sum --clock-control none --launch-
 PIB_GRAPHS=0 ncu --profile-from-start off --metrics gpu__time_duration.sum --clock-control none --csv --log-file $O/launches_${R}_pass_b4.csv \
     python tools/profile_step.py --config 70b --batch 4 > $O/ncu_pass_${R}.log 2>&1; echo "ncu pass rc=$?"
 # full sections for the matmul kernels of two layers
-PIB_GRAPHS=0 ncu --profile-from-start off --set full --clock-control none --import-source on -k regex:gemv_q4k_direct -c 8 -f -o $O/prof_${R}_gemv \
+PIB_GRAPHS=0 ncu --profile-from-start off --set full --clock-control none -k regex:gemv_q4k_direct -c 8 -f -o $O/prof_${R}_gemv \
     python tools/profile_step.py --config 70b --batch 4 --layers 2 > $O/ncu_full_${R}.log 2>&1; echo "ncu full rc=$?"
 ls -la $O | tail -12

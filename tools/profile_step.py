@@ -3,7 +3,7 @@
 
   ncu --profile-from-start off --metrics gpu__time_duration.sum --clock-control none --csv --log-file gpurun_out/launches.csv \
       python tools/profile_step.py --config 70b --batch 4
-  ncu --profile-from-start off --set full --clock-control none --import-source on -k regex:gemv -c 3 -o gpurun_out/prof \
+  ncu --profile-from-start off --set full --clock-control none -k regex:gemv -c 3 -o gpurun_out/prof \
       python tools/profile_step.py --config 70b --batch 4 --layers 2
 """
 import argparse
