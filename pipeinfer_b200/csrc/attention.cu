@@ -29,6 +29,15 @@
 void rope_table_build(std::vector<float2> & tab, int n_pos, int n_dims, int mode, float freq_base, float freq_scale) {
     const float theta_scale = powf(freq_base, -2.0f / n_dims);
     tab.resize((size_t) n_pos * (n_dims / 2));
+    if (mode & 4) {
+        // direct form: the angle of pair i at position p is p * base^(-2i / n_dims), each from its own power (no running product),
+        // evaluated in double and rounded once; pairs are (i, i + n_dims / 2)
+        for (int i = 0; i < n_dims / 2; i++) {
+            const double f = pow((double) freq_base, -2.0 * i / n_dims) * freq_scale;
+            for (int p = 0; p < n_pos; p++) tab[(size_t) p * (n_dims / 2) + i] = make_float2((float) cos(p * f), (float) sin(p * f));
+        }
+        return;
+    }
     for (int p = 0; p < n_pos; p++) {
         float theta_base = (float) p;
         if (mode & 2) theta_base *= freq_scale;

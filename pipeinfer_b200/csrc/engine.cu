@@ -12,6 +12,7 @@
 //   Wgate|Wup GEMV -> silu(gate)*up -> quantise -> Wdown   (K1 + K8 + K2 + K1)
 // then final RMSNorm -> lm_head GEMV -> argmax/top-8 on the device (K10).
 #include "engine.cuh"
+#include "hybrid.cuh"
 #include "gguf.cuh"
 
 #include <math.h>
@@ -378,6 +379,7 @@ pib_model * pib_model_synthetic(int n_layer, int n_embd, int n_head, int n_head_
 
 void pib_model_free(pib_model * m) {
     if (!m) return;
+    pib_hybrid_model_free(m);
     pib_weight_free(m->tok_embd);
     pib_weight_free(m->output);
     if (m->output_norm) cudaFree(m->output_norm);
@@ -395,7 +397,10 @@ void pib_model_free(pib_model * m) {
 // context
 #define CK(expr) do { if ((expr) != cudaSuccess) { pib_set_error("%s:%d %s: %s", __FILE__, __LINE__, #expr, cudaGetErrorString(cudaGetLastError())); goto fail; } } while (0)
 
+static pib_context * hybrid_context_new(pib_model * m, uint32_t n_ctx, int max_seq, pib_stage stage);
+
 pib_context * pib_context_new(pib_model * m, uint32_t n_ctx, int max_seq, pib_stage stage) {
+    if (m->hy) return hybrid_context_new(m, n_ctx, max_seq, stage);
     if (!pib_attention_supported(m->head_dim(), m->n_head, m->n_head_kv, (int) n_ctx)) {
         pib_set_error("context: head_dim %d / n_head %d / n_head_kv %d / n_ctx %u not supported by the attention kernel",
                       m->head_dim(), m->n_head, m->n_head_kv, n_ctx);
@@ -468,9 +473,49 @@ fail:
     return nullptr;
 }
 
+// a layer-list model's context: the common parts (streams, cell bookkeeping, cancel block, run table) without the llama work
+// buffers; state slots, latent cache and scratch come from pib_hybrid_ctx_init.  One stage only.
+static pib_context * hybrid_context_new(pib_model * m, uint32_t n_ctx, int max_seq, pib_stage stage) {
+    if (stage.size > 1) { pib_set_error("context: layer-list models run on one pipeline stage"); return nullptr; }
+    if (n_ctx == 0 || n_ctx > (1u << 24)) { pib_set_error("context: n_ctx %u", n_ctx); return nullptr; }
+    pib_context * c = new pib_context();
+    c->model = m; c->n_ctx = n_ctx; c->max_seq = max_seq < 1 ? 1 : max_seq; c->n_words = (c->max_seq + 31) / 32; c->stage = stage;
+    c->t_start_us = now_us();
+    int lo, hi, n_slots;
+    CK(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+    CK(cudaStreamCreateWithPriority(&c->stream, cudaStreamNonBlocking, lo));
+    CK(cudaStreamCreateWithPriority(&c->ctrl, cudaStreamNonBlocking, hi));
+    CK(cudaEventCreateWithFlags(&c->cancel_ev, cudaEventDisableTiming));
+    c->kv.init(n_ctx, c->max_seq);
+    if (kv_device_init(&c->kvd, n_ctx, c->n_words) != PIB_OK) goto fail;
+    CK(cudaMalloc(&c->cancel_table, 128 * sizeof(int)));
+    CK(cudaMemset(c->cancel_table, 0, 128 * sizeof(int)));
+    c->cancel_one = c->cancel_table + 100;
+    { int one = 1; CK(cudaMemcpy(c->cancel_one, &one, 4, cudaMemcpyHostToDevice)); }
+    CK(cudaMallocHost(&c->run_id_host, 64 * sizeof(int)));
+    for (int i = 0; i < 64; i++) c->run_id_host[i] = i;
+    c->desc_stride = pib_desc_stride(c->n_words);
+    c->desc_slots  = 1;                                   // one zeroed descriptor: the sampler's launch contract
+    CK(cudaMalloc(&c->desc_dev, c->desc_stride * 2));
+    CK(cudaMemset(c->desc_dev, 0, c->desc_stride * 2));
+    c->use_graphs = false;
+    c->ops_cap = 1 << 12;
+    CK(cudaMallocHost(&c->ops_host, sizeof(KvOp) * c->ops_cap));
+    CK(cudaMalloc(&c->ops_dev, sizeof(KvOp) * c->ops_cap));
+    c->runs.resize(64);
+    for (int i = 0; i < (int) c->runs.size(); i++) c->runs[i].id = i;
+    { const char * e = getenv("PIB_STATE_SLOTS"); n_slots = e ? atoi(e) : (c->max_seq < 8 ? c->max_seq : 8); }
+    if (pib_hybrid_ctx_init(c, n_slots) != PIB_OK) goto fail;
+    return c;
+fail:
+    pib_context_free(c);
+    return nullptr;
+}
+
 void pib_context_free(pib_context * c) {
     if (!c) return;
     if (c->stream) cudaStreamSynchronize(c->stream);
+    pib_hybrid_ctx_free(c);
     pib_pipe_hop_free(c);
     for (void * b : { (void *) c->pb.x, (void *) c->pb.x2, (void *) c->pb.qkv, (void *) c->pb.att, (void *) c->pb.proj, (void *) c->pb.gu,
                       (void *) c->pb.mask, c->pb.act, c->pb.xhat }) if (b) cudaFree(b);
@@ -500,7 +545,11 @@ void pib_context_free(pib_context * c) {
 // ---------------------------------------------------------------------------------------------------------------------
 // KV op-log front end: see kvlog_* in kv_meta.cu (lazy, coalescing; shared with the CPU-only test hooks)
 void pib_kv_push(pib_context * c, const KvOp & op) { kvlog_push(c->pending, op); }
-void pib_kv_flush_host(pib_context * c) { kvlog_flush(c->kv, c->pending, c->devops); }
+void pib_kv_flush_host(pib_context * c) {
+    if (c->hy) pib_hybrid_on_kv_ops(c, c->pending);           // state slots follow the same ops as the cells
+    kvlog_flush(c->kv, c->pending, c->devops);
+    if (c->hy) c->devops.clear();                             // no device replica of the cell table: kernels go through the slots' position -> cell tables
+}
 static std::vector<KvOp> & devq(pib_context * c) { return c->devops; }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -874,7 +923,7 @@ static int run_prompt_pass(pib_context * c, pib_run & run, int ch0, int nch, int
     return PIB_OK;
 }
 
-static pib_run * take_run(pib_context * c, int n_tokens) {
+pib_run * pib_take_run(pib_context * c, int n_tokens) {
     for (auto & r : c->runs) {
         if (r.in_use || r.id == c->last_finished) continue;
         if (!r.done) cudaEventCreateWithFlags(&r.done, cudaEventDisableTiming);
@@ -908,6 +957,7 @@ static bool slow_trace() { static int on = -1; if (on < 0) on = getenv("PIB_TRAC
 int pib_decode_start(pib_context * c, int n_tokens, const int32_t * token, const int32_t * pos, const int32_t * n_seq_id,
                      const int32_t * const * seq_id, int batch_id) {
     if (n_tokens <= 0) { pib_set_error("decode: n_tokens == 0"); return -1; }
+    if (c->hy) return pib_hybrid_decode_start(c, n_tokens, token, pos, n_seq_id, seq_id, batch_id);
     int64_t t_mark = slow_trace() ? now_us() : 0;
     pib_model * m = c->model;
     pib_kv_flush_host(c);
@@ -927,7 +977,7 @@ int pib_decode_start(pib_context * c, int n_tokens, const int32_t * token, const
     // llama.cpp:5548-5571: head-reset heuristic, find_slot, attended range n
     const bool found = kvlog_decode_begin(c->kv, dq, n_tokens, pos, tb.data());
     SLOW_MARK("find slot");
-    pib_run *  run   = found ? take_run(c, n_tokens) : nullptr;
+    pib_run *  run   = found ? pib_take_run(c, n_tokens) : nullptr;
     SLOW_MARK("take run");
     if (!found) pib_set_error("decode: no KV slot for %d tokens", n_tokens);
     if (!run) return -1;      // bookkeeping done so far (flushed ops, head moves) stays queued for the device
@@ -1060,7 +1110,7 @@ int pib_decode_replay(pib_context * c, int batch_id, int n_tokens, int n_chunks,
         q.insert(q.end(), ops, ops + n_ops);
         return pib_apply_devops(c);
     }
-    pib_run * run = take_run(c, n_tokens);
+    pib_run * run = pib_take_run(c, n_tokens);
     if (!run) return PIB_ERR_NOMEM;
     std::vector<int> slots(n_chunks);
     for (int ch = 0; ch < n_chunks; ch++) {

@@ -42,12 +42,16 @@ struct pib_layer {
     pib_weight * wdown     = nullptr;
 };
 
+struct pib_hybrid;                 // hybrid.cuh: the layer list of a model whose layers name their own mixer and feed-forward
+struct pib_hybrid_ctx;             // hybrid.cuh: its state slots, latent cache and work buffers
+
 struct pib_model {
+    pib_hybrid * hy = nullptr;           // set for arch 2 (layer-list models loaded from a folder); the llama / falcon fields below stay unused
     // hyper-parameters (reference llm_load_hparams, llama.cpp:2203-2290)
     int   n_layer = 0, n_embd = 0, n_head = 0, n_head_kv = 0, n_ff = 0, n_vocab = 0, n_rot = 0, n_ctx_train = 0;
     float rms_eps = 1e-5f, rope_freq_base = 10000.f, rope_freq_scale = 1.f;
     int   wtype = 0;
-    int   arch = 0;                      // 0 llama (build_llama, llama.cpp:3872), 1 falcon (build_falcon, :4106)
+    int   arch = 0;                      // 0 llama (build_llama, llama.cpp:3872), 1 falcon (build_falcon, :4106), 2 layer list (hybrid.cuh)
     float norm_eps = 1e-5f;              // falcon: f_norm_eps
     int   tok_bos = 1, tok_eos = 2;
     // tensors (only those of the layer range this process owns are resident)
@@ -94,6 +98,7 @@ struct pib_stage {                 // pipeline position of this process (1-GPU: 
 };
 
 struct pib_context {
+    pib_hybrid_ctx * hy  = nullptr;       // layer-list models: state slots, latent cache, batch bookkeeping (hybrid.cu)
     pib_model *  model   = nullptr;
     uint32_t     n_ctx   = 0;
     int          max_seq = 1;

@@ -1,0 +1,326 @@
+// hybrid.cu -- contexts and the decode step of layer-list models (hybrid.cuh).
+//
+// A decode takes a llama_batch like every other model's: tokens of several sequences, each sequence's tokens in order and next to
+// each other (a "segment": a portion of a prompt, or one decoded token).  The step
+//   1. resolves a state slot for every segment (SeqSlots) and a cell for every token (KvMirror::find_cells) on the host,
+//   2. ships the batch's bookkeeping in one copy (token, position, cell, slot, segment per token; start / length / slot per segment),
+//   3. runs every layer over ALL tokens of the batch at once: matmuls see one [tokens x width] operand, the attention kernel finds
+//      a token's keys through its slot's position -> cell table, the recurrences walk each segment from the slot's state,
+//   4. leaves logits rows and the sampler's top-8 records where the other architectures leave them (pib_run).
+// Nothing depends on how a prompt was cut into segments, on the other segments of the batch, or on which cells / slots were used,
+// beyond the summation order inside the matmuls.
+#include "hybrid.cuh"
+
+#include <algorithm>
+
+int  pib_sample_topk(float * logits_dev, int n_rows, int n_vocab, const int32_t * bias_ids_dev, const float * bias_val_dev, int n_bias,
+                     void * out_dev, const uint8_t * desc, const int * cancel, cudaStream_t st);
+void rope_table_build(std::vector<float2> & tab, int n_pos, int n_dims, int mode, float freq_base, float freq_scale);
+
+struct pib_hybrid_ctx {
+    SeqSlots slots;
+    float *   state = nullptr;                  // [n_slots][state_floats]
+    int32_t * cellmap = nullptr;                // [n_slots][n_ctx]
+    std::vector<float *>  cache;                // per caching layer: [n_ctx][cache_row]
+    std::vector<float2 *> rope;                 // per rotation: [n_ctx][dims / 2] {cos, sin}
+    // scratch, sized for cap tokens
+    int cap = 0;
+    float * x = nullptr, * h = nullptr, * y = nullptr, * proj = nullptr, * cq = nullptr, * q = nullptr, * qlat = nullptr, * lat = nullptr, * att = nullptr;
+    float * rlog = nullptr, * wts = nullptr, * eup = nullptr, * edn = nullptr, * ysh = nullptr;
+    int32_t * ids = nullptr, * perm = nullptr, * inv = nullptr, * counts = nullptr, * offs = nullptr;
+    // batch bookkeeping: pinned staging ring + device copy
+    static const int RING = 4;
+    int32_t *   meta_host[RING] = { nullptr, nullptr, nullptr, nullptr };
+    cudaEvent_t meta_ev[RING]   = { nullptr, nullptr, nullptr, nullptr };
+    int32_t *   meta_dev = nullptr;
+    int         meta_cap = 0, meta_next = 0;
+    std::string kv_error;                       // set when a cache op arrived that the states cannot follow
+};
+
+#define HCK(expr) do { if ((expr) != cudaSuccess) { pib_set_error("%s:%d %s: %s", __FILE__, __LINE__, #expr, cudaGetErrorString(cudaGetLastError())); return PIB_ERR_CUDA; } } while (0)
+
+int pib_hybrid_ctx_init(pib_context * c, int n_slots) {
+    const pib_hybrid * hy = c->model->hy;
+    pib_hybrid_ctx * x = new pib_hybrid_ctx();
+    c->hy = x;
+    if (n_slots < 1) n_slots = 1;
+    x->slots.init(n_slots);
+    HCK(cudaMalloc(&x->state, (size_t) n_slots * hy->state_floats * 4));
+    HCK(cudaMemset(x->state, 0, (size_t) n_slots * hy->state_floats * 4));
+    HCK(cudaMalloc(&x->cellmap, (size_t) n_slots * c->n_ctx * 4));
+    HCK(cudaMemset(x->cellmap, 0, (size_t) n_slots * c->n_ctx * 4));
+    x->cache.assign((size_t) hy->n_cache, nullptr);
+    for (int i = 0; i < hy->n_cache; i++) {
+        HCK(cudaMalloc(&x->cache[i], (size_t) c->n_ctx * hy->cache_row[i] * 4));
+        HCK(cudaMemset(x->cache[i], 0, (size_t) c->n_ctx * hy->cache_row[i] * 4));
+    }
+    x->rope.assign(hy->ropes.size(), nullptr);
+    for (size_t i = 0; i < hy->ropes.size(); i++) {
+        std::vector<float2> tab;
+        rope_table_build(tab, (int) c->n_ctx, hy->ropes[i].dims, 4, hy->ropes[i].base, 1.0f);         // mode 4: every angle from its own power, in double
+        HCK(cudaMalloc(&x->rope[i], std::max<size_t>(16, tab.size() * sizeof(float2))));
+        HCK(cudaMemcpy(x->rope[i], tab.data(), tab.size() * sizeof(float2), cudaMemcpyHostToDevice));
+    }
+    return PIB_OK;
+}
+
+// another number of state slots; only before the first decode of the context
+int pib_hybrid_set_slots(pib_context * c, int n_slots) {
+    pib_hybrid_ctx * x = c->hy;
+    if (!x || n_slots < 1 || c->n_decode != 0) { pib_set_error("state slots: needs a layer-list model's context that has not decoded yet"); return PIB_ERR_ARG; }
+    const pib_hybrid * hy = c->model->hy;
+    cudaStreamSynchronize(c->stream);
+    cudaFree(x->state); cudaFree(x->cellmap);
+    x->state = nullptr; x->cellmap = nullptr;
+    x->slots.init(n_slots);
+    HCK(cudaMalloc(&x->state, (size_t) n_slots * hy->state_floats * 4));
+    HCK(cudaMemset(x->state, 0, (size_t) n_slots * hy->state_floats * 4));
+    HCK(cudaMalloc(&x->cellmap, (size_t) n_slots * c->n_ctx * 4));
+    HCK(cudaMemset(x->cellmap, 0, (size_t) n_slots * c->n_ctx * 4));
+    return PIB_OK;
+}
+int pib_hybrid_slots_free(const pib_context * c) { return c->hy ? c->hy->slots.n_free() : 0; }
+
+static void free_scratch(pib_hybrid_ctx * x) {
+    for (void * b : { (void *) x->x, (void *) x->h, (void *) x->y, (void *) x->proj, (void *) x->cq, (void *) x->q, (void *) x->qlat, (void *) x->lat, (void *) x->att,
+                      (void *) x->rlog, (void *) x->wts, (void *) x->eup, (void *) x->edn, (void *) x->ysh, (void *) x->ids, (void *) x->perm, (void *) x->inv,
+                      (void *) x->counts, (void *) x->offs }) if (b) cudaFree(b);
+    x->x = x->h = x->y = x->proj = x->cq = x->q = x->qlat = x->lat = x->att = x->rlog = x->wts = x->eup = x->edn = x->ysh = nullptr;
+    x->ids = x->perm = x->inv = x->counts = x->offs = nullptr;
+    x->cap = 0;
+}
+
+void pib_hybrid_ctx_free(pib_context * c) {
+    pib_hybrid_ctx * x = c->hy;
+    if (!x) return;
+    free_scratch(x);
+    if (x->state) cudaFree(x->state);
+    if (x->cellmap) cudaFree(x->cellmap);
+    for (float * p : x->cache) if (p) cudaFree(p);
+    for (float2 * p : x->rope) if (p) cudaFree(p);
+    for (int i = 0; i < pib_hybrid_ctx::RING; i++) { if (x->meta_host[i]) cudaFreeHost(x->meta_host[i]); if (x->meta_ev[i]) cudaEventDestroy(x->meta_ev[i]); }
+    if (x->meta_dev) cudaFree(x->meta_dev);
+    delete x;
+    c->hy = nullptr;
+}
+
+void pib_hybrid_on_kv_ops(pib_context * c, const std::vector<KvOp> & ops) {
+    for (const KvOp & op : ops)
+        if (!c->hy->slots.apply(op) && c->hy->kv_error.empty())
+            c->hy->kv_error = "a sequence with recurrent state was copied or partly removed (op " + std::to_string(op.op) + "): its state cannot follow";
+}
+
+static int grow_scratch(pib_context * c, int T) {
+    pib_hybrid_ctx * x = c->hy;
+    if (T <= x->cap) return PIB_OK;
+    const pib_hybrid * hy = c->model->hy;
+    cudaStreamSynchronize(c->stream);
+    free_scratch(x);
+    const size_t n = (size_t) ((T + 63) / 64 * 64), W = (size_t) c->model->n_embd;
+    auto fl = [&](float ** p, size_t per) { return per == 0 || cudaMalloc(p, n * per * 4) == cudaSuccess; };
+    auto in = [&](int32_t ** p, size_t cnt) { return cnt == 0 || cudaMalloc(p, cnt * 4) == cudaSuccess; };
+    const bool ok = fl(&x->x, W) && fl(&x->h, W) && fl(&x->y, W) && fl(&x->proj, (size_t) hy->w_proj) && fl(&x->cq, (size_t) hy->w_cq) && fl(&x->q, (size_t) hy->w_q) &&
+                    fl(&x->qlat, (size_t) hy->w_lat) && fl(&x->lat, (size_t) hy->w_lat) && fl(&x->att, (size_t) hy->w_att) && fl(&x->rlog, (size_t) hy->w_router) &&
+                    fl(&x->wts, (size_t) hy->w_pairs) && fl(&x->eup, (size_t) hy->w_eup) && fl(&x->edn, (size_t) hy->w_pairs * W) && fl(&x->ysh, hy->w_pairs ? W : 0) &&
+                    in(&x->ids, n * hy->w_pairs) && in(&x->perm, n * hy->w_pairs) && in(&x->inv, n * hy->w_pairs) && in(&x->counts, (size_t) hy->w_router + 1) &&
+                    in(&x->offs, (size_t) hy->w_router + 2);
+    if (!ok) { cudaGetLastError(); free_scratch(x); pib_set_error("decode: out of memory for the work buffers of %d tokens", T); return PIB_ERR_NOMEM; }
+    x->cap = (int) n;
+    return PIB_OK;
+}
+
+// ---- the layers -----------------------------------------------------------------------------------------------------------------------
+static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B) {
+    pib_hybrid_ctx *   x  = c->hy;
+    const pib_model *  m  = c->model;
+    const pib_hybrid * hy = m->hy;
+    cudaStream_t       st = c->stream;
+    const int   T = B.T, W = m->n_embd, exact = hy->dtype == PIB_TYPE_F32;
+    const float eps = hy->eps;
+    int rc;
+    uint64_t & nk = c->n_kernels;
+#define RC(e) do { rc = (e); if (rc != PIB_OK) return rc; nk++; } while (0)
+    auto mm = [&](const pib_weight * w, const float * X, int ldx, float * Y, int ldy, int epi) {
+        pib_mm a;
+        a.W = w->base; a.wtype = w->type; a.ldw = w->K; a.X = X; a.ldx = ldx; a.Y = Y; a.ldy = ldy; a.M = T; a.N = (int) w->N; a.K = (int) w->K; a.epi = epi;
+        a.exact = exact || w->type == PIB_TYPE_F32;
+        return pib_dense_mm(a, st);
+    };
+    RC(pib_cellmap_set(x->cellmap, (int) c->n_ctx, B, st));
+    RC(pib_embed_ln(m->tok_embd, B.tok, hy->embd_norm, eps, T, W, x->x, st));
+    for (int il = 0; il < m->n_layer; il++) {
+        const pib_hlayer & L = hy->layers[il];
+        const float * hin = x->x;
+        if (L.canon) { RC(pib_canon_conv(x->x, L.canon, hy->taps, B, x->state, hy->state_floats, L.tail_off, W, x->h, st)); nk += hy->taps > 1; hin = x->h; }
+        if (L.mixer == PIB_MIXER_LATENT) {
+            const int H = L.heads, D = L.dim, rd = L.rot_dim, R = L.kv_rank, V = L.vdim, ldp = (int) L.dqkv->N, row = hy->cache_row[L.cache_id];
+            float * cache = x->cache[L.cache_id];
+            RC(mm(L.dqkv, hin, W, x->proj, ldp, PIB_EPI_NONE));
+            RC(pib_latent_prep(x->proj, ldp, L, L.dq_norm, L.dkv_norm, eps, B, x->rope[L.rope_id], (int) c->n_ctx, x->cq, L.kv_from < 0 ? cache : nullptr, row, st));
+            RC(mm(L.uq, x->cq, L.q_rank, x->q, H * (D + rd), PIB_EPI_NONE));
+            {   // q_lat[t][h] = W_uk,h^T q_unrotated[t][h]: one problem per head
+                pib_mm a;
+                a.W = L.ukT->base; a.wtype = L.ukT->type; a.ldw = D; a.wz = (int64_t) R * D; a.X = x->q; a.ldx = (int64_t) H * (D + rd); a.xz = D + rd;
+                a.Y = x->qlat; a.ldy = (int64_t) H * R; a.yz = R; a.M = T; a.N = R; a.K = D; a.Z = H; a.exact = exact;
+                RC(pib_dense_mm(a, st));
+            }
+            RC(pib_latent_attention(x->q, x->qlat, L, B, x->rope[L.rope_id], (int) c->n_ctx, cache, row, x->cellmap, (int) c->n_ctx, x->lat, st));
+            {   // value of head h = W_uv,h (sum_j p_j c_j)
+                pib_mm a;
+                a.W = L.uv->base; a.wtype = L.uv->type; a.ldw = R; a.wz = (int64_t) V * R; a.X = x->lat; a.ldx = (int64_t) H * R; a.xz = R;
+                a.Y = x->att; a.ldy = (int64_t) H * V; a.yz = V; a.M = T; a.N = V; a.K = R; a.Z = H; a.exact = exact;
+                RC(pib_dense_mm(a, st));
+            }
+            RC(mm(L.wo, x->att, H * V, x->y, W, PIB_EPI_NONE));
+        } else {
+            const int H = L.heads, HD = H * L.dim, ldp = (int) L.qfv->N;
+            RC(mm(L.qfv, hin, W, x->proj, ldp, PIB_EPI_NONE));
+            RC(pib_hgrn2_gates(x->proj, ldp, L.f_bias, L.lower, T, HD, st));
+            RC(pib_hgrn2_scan(x->proj, ldp, L, B, x->state, hy->state_floats, L.onorm, eps, x->att, st)); nk++;
+            RC(mm(L.wo, x->att, H * L.vdim, x->y, W, PIB_EPI_NONE));
+        }
+        RC(pib_layer_norm(x->y, L.norm1, eps, T, W, x->x, 1, st));
+        if (L.mlp == PIB_MLP_POLYNORM) {
+            RC(mm(L.up, x->x, W, x->proj, L.ff, PIB_EPI_NONE));
+            RC(pib_polynorm(x->proj, T, L.ff, L.act, eps, st));
+            RC(mm(L.down, x->proj, L.ff, x->y, W, PIB_EPI_NONE));
+            RC(pib_layer_norm(x->y, L.norm2, eps, T, W, x->x, 1, st));
+        } else if (L.mlp == PIB_MLP_MOE) {
+            const int E = L.n_experts, top = L.top, P = T * top;
+            RC(mm(L.router, x->x, W, x->rlog, E, PIB_EPI_NONE));
+            RC(pib_moe_route(x->rlog, T, E, top, x->ids, x->wts, st));
+            RC(pib_moe_sort(x->ids, P, E, x->counts, x->offs, x->perm, x->inv, st)); nk++;
+            {   // up-projection of every (token, expert) pair, pairs grouped by expert; relu^2 on the way out
+                pib_mm a;
+                a.W = L.e_up->base; a.wtype = L.e_up->type; a.ldw = W; a.wz = (int64_t) L.ff_e * W; a.X = x->x; a.ldx = W; a.xrows = x->perm; a.xdiv = top;
+                a.Y = x->eup; a.ldy = L.ff_e; a.M = P; a.N = L.ff_e; a.K = W; a.Z = E; a.zrange = x->offs; a.epi = PIB_EPI_RELU2; a.exact = exact;
+                RC(pib_dense_mm(a, st));
+                pib_mm b;
+                b.W = L.e_down->base; b.wtype = L.e_down->type; b.ldw = L.ff_e; b.wz = (int64_t) W * L.ff_e; b.X = x->eup; b.ldx = L.ff_e;
+                b.Y = x->edn; b.ldy = W; b.M = P; b.N = W; b.K = L.ff_e; b.Z = E; b.zrange = x->offs; b.exact = exact;
+                RC(pib_dense_mm(b, st));
+            }
+            if (L.s_up) {
+                RC(mm(L.s_up, x->x, W, x->proj, L.ff_s, PIB_EPI_RELU2));
+                RC(mm(L.s_down, x->proj, L.ff_s, x->ysh, W, PIB_EPI_NONE));
+            }
+            RC(pib_moe_combine(L.s_up ? x->ysh : nullptr, x->edn, x->wts, x->inv, T, top, W, x->y, st));
+            RC(pib_layer_norm(x->y, L.norm2, eps, T, W, x->x, 1, st));
+        }
+        if (const char * dump = getenv("PIB_HYBRID_DUMP")) {          // debugging: the residual stream after every layer, one file per layer and decode
+            std::vector<float> hb((size_t) T * W);
+            cudaMemcpyAsync(hb.data(), x->x, hb.size() * 4, cudaMemcpyDeviceToHost, st);
+            cudaStreamSynchronize(st);
+            char path[512];
+            snprintf(path, sizeof(path), "%s/d%llu_l%d.f32", dump, (unsigned long long) c->n_decode, il);
+            if (FILE * f = fopen(path, "wb")) { fwrite(hb.data(), 4, hb.size(), f); fclose(f); }
+        }
+    }
+    RC(pib_layer_norm(x->x, m->output_norm, eps, T, W, x->h, 0, st));
+    RC(mm(m->output, x->h, W, run.logits, m->n_vocab, PIB_EPI_NONE));
+    RC(pib_sample_topk(run.logits, T, m->n_vocab, c->bias_ids_dev, c->bias_val_dev, c->n_bias, run.res_dev, c->desc_dev, c->cancel_table, st));
+#undef RC
+    return PIB_OK;
+}
+
+// ---- decode -----------------------------------------------------------------------------------------------------------------------------
+int pib_hybrid_decode_start(pib_context * c, int n_tokens, const int32_t * token, const int32_t * pos, const int32_t * n_seq_id,
+                            const int32_t * const * seq_id, int batch_id) {
+    pib_hybrid_ctx *   x  = c->hy;
+    const pib_model *  m  = c->model;
+    const pib_hybrid * hy = m->hy;
+    pib_kv_flush_host(c);
+    if (!x->kv_error.empty()) { pib_set_error("decode: %s", x->kv_error.c_str()); return -1; }
+    const int T = n_tokens, W = c->n_words;
+    // segments: runs of one sequence with consecutive positions
+    struct Seg { int start, len, seq, slot; bool fresh; };
+    std::vector<Seg> segs;
+    for (int i = 0; i < T; i++) {
+        if (token[i] < 0 || token[i] >= m->n_vocab) { pib_set_error("decode: token id %d out of range", token[i]); return -1; }
+        if (n_seq_id[i] != 1) { pib_set_error("decode: a token of a model with per-sequence state belongs to exactly one sequence"); return -1; }
+        const int s = seq_id[i][0];
+        if (s < 0 || s >= W * 32) { pib_set_error("decode: sequence id %d out of range (max_seq %d)", s, c->max_seq); return -1; }
+        if (pos[i] < 0 || (uint32_t) pos[i] >= c->n_ctx) { pib_set_error("decode: position %d outside the context of %u", pos[i], c->n_ctx); return -1; }
+        if (!segs.empty() && segs.back().seq == s) {
+            if (pos[i] != pos[i - 1] + 1) { pib_set_error("decode: positions of sequence %d are not consecutive", s); return -1; }
+            segs.back().len++;
+        } else {
+            for (const Seg & g : segs) if (g.seq == s) { pib_set_error("decode: tokens of sequence %d are not next to each other in the batch", s); return -1; }
+            segs.push_back({ i, 1, s, -1, false });
+        }
+    }
+    int need = 0;
+    for (Seg & g : segs) {
+        g.slot = x->slots.find(g.seq);
+        const int have = g.slot >= 0 ? x->slots.len[(size_t) g.slot] : 0;
+        if (pos[g.start] != have) { pib_set_error("decode: sequence %d continues at position %d, the batch starts at %d", g.seq, have, pos[g.start]); return -1; }
+        if (g.slot < 0) need++;
+    }
+    if (need > x->slots.n_free()) { pib_set_error("decode: no state slot for %d new sequences (%d slots)", need, x->slots.n_slots()); return -1; }
+    // cells
+    std::vector<uint32_t> tb((size_t) T * W, 0u);
+    for (int i = 0; i < T; i++) tb[(size_t) i * W + (seq_id[i][0] >> 5)] |= 1u << (seq_id[i][0] & 31);
+    std::vector<int32_t> cells((size_t) T);
+    if (!c->kv.find_cells(T, pos, tb.data(), cells.data())) { pib_set_error("decode: no KV cells for %d tokens (%u of %u used)", T, c->kv.used, c->kv.size); return -1; }
+    const int32_t cm = c->kv.cell_max();
+    c->kv.n = (uint32_t) std::min<int32_t>((int32_t) c->kv.size, std::max<int32_t>(cm, 32));
+    pib_run * run = pib_take_run(c, T);
+    if (!run || grow_scratch(c, T) != PIB_OK) {
+        for (int i = 0; i < T; i++) { c->kv.pos[(size_t) cells[i]] = -1; memset(&c->kv.bits[(size_t) cells[i] * W], 0, (size_t) W * 4); }
+        c->kv.used -= (uint32_t) T;
+        return -1;
+    }
+    cudaStream_t st = c->stream;
+    for (Seg & g : segs) {
+        if (g.slot < 0) {
+            g.slot = x->slots.acquire(g.seq);
+            g.fresh = true;
+            cudaMemsetAsync(x->state + (size_t) g.slot * hy->state_floats, 0, hy->state_floats * 4, st);      // a new owner starts from zero
+        }
+        x->slots.len[(size_t) g.slot] += g.len;
+    }
+    // bookkeeping: [tok | pos | cell | slot | seg] x T, then [seg_start | seg_len | seg_slot] x S
+    const int S = (int) segs.size(), words = 5 * T + 3 * S;
+    if (words > x->meta_cap) {
+        cudaStreamSynchronize(st);
+        for (int i = 0; i < pib_hybrid_ctx::RING; i++) { if (x->meta_host[i]) cudaFreeHost(x->meta_host[i]); x->meta_host[i] = nullptr; }
+        if (x->meta_dev) cudaFree(x->meta_dev);
+        x->meta_cap = words * 2 + 64;
+        bool ok = cudaMalloc(&x->meta_dev, (size_t) x->meta_cap * 4) == cudaSuccess;
+        for (int i = 0; ok && i < pib_hybrid_ctx::RING; i++) {
+            ok = cudaMallocHost(&x->meta_host[i], (size_t) x->meta_cap * 4) == cudaSuccess;
+            if (ok && !x->meta_ev[i]) ok = cudaEventCreateWithFlags(&x->meta_ev[i], cudaEventDisableTiming) == cudaSuccess;
+        }
+        if (!ok) { cudaGetLastError(); x->meta_cap = 0; pib_set_error("decode: out of memory for the batch bookkeeping"); return -1; }
+    }
+    const int ring = x->meta_next;
+    x->meta_next = (x->meta_next + 1) % pib_hybrid_ctx::RING;
+    cudaEventSynchronize(x->meta_ev[ring]);
+    int32_t * mh = x->meta_host[ring];
+    for (int sgi = 0; sgi < S; sgi++) {
+        const Seg & g = segs[(size_t) sgi];
+        for (int i = g.start; i < g.start + g.len; i++) { mh[3 * T + i] = g.slot; mh[4 * T + i] = sgi; }
+        mh[5 * T + sgi] = g.start; mh[5 * T + S + sgi] = g.len; mh[5 * T + 2 * S + sgi] = g.slot;
+    }
+    memcpy(mh, token, (size_t) T * 4);
+    memcpy(mh + T, pos, (size_t) T * 4);
+    memcpy(mh + 2 * T, cells.data(), (size_t) T * 4);
+    cudaMemcpyAsync(x->meta_dev, mh, (size_t) words * 4, cudaMemcpyHostToDevice, st);
+    cudaEventRecord(x->meta_ev[ring], st);
+    c->h2d_bytes += (size_t) words * 4;
+    const int32_t * md = x->meta_dev;
+    pib_hbatch B = { md, md + T, md + 2 * T, md + 3 * T, md + 4 * T, md + 5 * T, md + 5 * T + S, md + 5 * T + 2 * S, T, S };
+    run->in_use = true; run->batch_id = batch_id; run->n_tokens = T; run->failed = false; run->has_walk = false;
+    c->tree_pending.n_branches = 0;
+    cudaMemcpyAsync(c->cancel_table, c->run_id_host + run->id, sizeof(int), cudaMemcpyHostToDevice, st);
+    if (run_layers(c, *run, B) != PIB_OK) run->failed = true;
+    if (!run->failed) {
+        cudaMemcpyAsync(run->res_host, run->res_dev, sizeof(pib_row_result) * (size_t) T, cudaMemcpyDeviceToHost, st);
+        c->d2h_bytes += sizeof(pib_row_result) * (size_t) T;
+        run->rows_on_host = true;
+    }
+    cudaEventRecord(run->done, st);
+    c->inflight.push_back(run->id);
+    c->n_decode++;
+    return run->id;
+}

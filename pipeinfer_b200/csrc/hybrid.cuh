@@ -1,0 +1,112 @@
+// hybrid.cuh -- layer-list models: every layer names its own mixer (windowed latent attention with a sink, or the gated linear
+// recurrence HGRN2) and its own feed-forward (dense with a PolyNorm activation, or a routed mixture of experts with a shared expert).
+// The first design built from these parts is "Rapisun"; the parts take their sizes and constants as parameters so that another
+// layer-list design can name them too.
+//
+// What such a model adds to the runtime, beside what llama / falcon graphs use:
+//   * dense weights (bfloat16 or float32 rows, pib_weight with type PIB_TYPE_BF16 / PIB_TYPE_F32) and the matmul for them (dense_mm.cu);
+//   * a per-sequence STATE SLOT (SeqSlots, kv_meta.cuh): the recurrent matrices, the tails of the short convolutions and the
+//     position -> cell table of the sequence.  A slot is taken at a sequence's first token and given back by llama_kv_cache_seq_rm of the
+//     whole sequence (or _clear / _seq_keep);
+//   * KV cells that hold one latent row per caching layer instead of K and V rows; cells are handed out one by one (scattered), so
+//     a batch needs no contiguous run of free cells.
+#pragma once
+
+#include "engine.cuh"
+
+enum { PIB_MIXER_LATENT = 1, PIB_MIXER_HGRN2 = 2 };
+enum { PIB_MLP_NONE = 0, PIB_MLP_POLYNORM = 1, PIB_MLP_MOE = 2 };
+enum { PIB_EPI_NONE = 0, PIB_EPI_RELU2 = 1 };
+
+struct pib_hlayer {
+    int     mixer = 0, mlp = 0;
+    float * norm1 = nullptr, * norm2 = nullptr;      // LayerNorm weights applied to the sublayers' OUTPUTS
+    float * canon = nullptr;                          // [width][taps] causal convolution in front of the mixer (null: none)
+    // ---- latent attention ----
+    int   heads = 0, dim = 0, rot_dim = 0, vdim = 0, kv_rank = 0, q_rank = 0, window = 0, rot_dims = 0;
+    float rot_base = 10000.f, scale = 1.f;
+    int   kv_from = -1;                               // layer whose cache rows this layer reads (-1: its own)
+    int   cache_id = -1;                              // index among the layers that own cache rows
+    int   rope_id = -1;                               // index of the rotation table (distinct base / dims)
+    pib_weight * dqkv = nullptr;                      // rows: W_dq (q_rank) | W_dkv (kv_rank + rot_dim, absent when kv_from >= 0)
+    pib_weight * uq = nullptr, * ukT = nullptr, * uv = nullptr, * wo = nullptr;   // ukT: per head [kv_rank][dim] (W_uk transposed)
+    float * dq_norm = nullptr, * dkv_norm = nullptr, * sink = nullptr;
+    // ---- HGRN2 ----
+    pib_weight * qfv = nullptr;                       // rows: W_q (heads*dim) | W_f (heads*dim) | W_v (heads*vdim)
+    float * f_bias = nullptr, * lower = nullptr, * onorm = nullptr;
+    size_t  state_off = 0;                            // floats into a slot's state: the recurrent matrices [heads][dim][vdim]
+    size_t  tail_off = 0;                             // floats into a slot's state: the convolution's last taps-1 inputs [taps-1][width]
+    // ---- feed-forward ----
+    int   ff = 0;
+    pib_weight * up = nullptr, * down = nullptr;
+    float act[4] = { 0, 0, 0, 0 };
+    int   n_experts = 0, top = 0, ff_e = 0, ff_s = 0;
+    pib_weight * e_up = nullptr, * e_down = nullptr;  // experts stacked: [E * ff_e][width], [E * width][ff_e]
+    pib_weight * router = nullptr;                    // always float32
+    pib_weight * s_up = nullptr, * s_down = nullptr;
+};
+
+struct pib_hybrid {
+    int     dtype = PIB_TYPE_BF16;                    // PIB_TYPE_BF16: matmul operands rounded to bfloat16, fp32 accumulation; PIB_TYPE_F32: all fp32
+    int     taps = 1;
+    float   eps = 1e-5f;
+    float * embd_norm = nullptr;
+    std::vector<pib_hlayer> layers;
+    size_t  state_floats = 0;                         // per state slot
+    int     n_cache = 0;
+    std::vector<int> cache_row;                       // floats per cell of caching layer i
+    struct Rope { float base; int dims; };
+    std::vector<Rope> ropes;
+    // widest per-token scratch rows over all layers
+    int     w_proj = 0, w_cq = 0, w_q = 0, w_lat = 0, w_att = 0, w_pairs = 0, w_eup = 0, w_router = 0;
+};
+
+struct pib_hybrid_ctx;
+pib_model * pib_model_load_dir(const char * dir, int dtype);          // model_dir.cu: config.json + model.safetensors
+pib_model * pib_hybrid_synthetic(const char * config_json, uint64_t seed, int dtype);   // random weights for a configuration (bench)
+void        pib_hybrid_model_free(pib_model * m);
+int         pib_hybrid_ctx_init(pib_context * c, int n_slots);
+void        pib_hybrid_ctx_free(pib_context * c);
+int         pib_hybrid_set_slots(pib_context * c, int n_slots);
+int         pib_hybrid_slots_free(const pib_context * c);
+void        pib_hybrid_on_kv_ops(pib_context * c, const std::vector<KvOp> & ops);
+int         pib_hybrid_decode_start(pib_context * c, int n_tokens, const int32_t * token, const int32_t * pos, const int32_t * n_seq_id,
+                                    const int32_t * const * seq_id, int batch_id);
+pib_run *   pib_take_run(pib_context * c, int n_tokens);               // engine.cu
+
+// dense_mm.cu -- Y[z][m][n] (op)= sum_k X[z][row(m)][k] * W[z][n][k]
+struct pib_mm {
+    const void *    W = nullptr; int wtype = PIB_TYPE_BF16; int64_t ldw = 0, wz = 0;
+    const float *   X = nullptr; int64_t ldx = 0, xz = 0;
+    const int32_t * xrows = nullptr; int xdiv = 1;       // row m reads X row xrows[m] / xdiv (null: m)
+    float *         Y = nullptr; int64_t ldy = 0, yz = 0;
+    int             M = 0, N = 0, K = 0, Z = 1;
+    const int32_t * zrange = nullptr;                    // device [Z + 1]: z owns rows [zrange[z], zrange[z + 1]); null: all M rows, every z
+    int             epi = PIB_EPI_NONE;
+    int             exact = 0;                           // 1: operands stay fp32 (no bfloat16 rounding of X); W must be float32
+};
+int pib_dense_mm(const pib_mm & a, cudaStream_t st);
+pib_weight * pib_dense_upload(int type, const void * host, int64_t N, int64_t K);   // type: PIB_TYPE_BF16 / PIB_TYPE_F32, row-major [N][K]
+
+// hybrid_kernels.cu
+struct pib_hbatch {                  // device view of one batch's bookkeeping
+    const int32_t * tok, * pos, * cell, * slot, * seg;       // [T]
+    const int32_t * seg_start, * seg_len, * seg_slot;         // [S]
+    int T, S;
+};
+int pib_embed_ln(const pib_weight * embd, const int32_t * tok, const float * w, float eps, int T, int W, float * x, cudaStream_t st);
+int pib_layer_norm(const float * in, const float * w, float eps, int T, int W, float * out, int accumulate, cudaStream_t st);
+int pib_canon_conv(const float * x, const float * w, int taps, const pib_hbatch & b, float * state, size_t state_stride, size_t tail_off, int W, float * h,
+                   cudaStream_t st);
+int pib_latent_prep(const float * proj, int ldp, const pib_hlayer & L, const float * dq_norm, const float * dkv_norm, float eps, const pib_hbatch & b,
+                    const float2 * rope, int rope_n_pos, float * cq, float * cache, int cache_row, cudaStream_t st);
+int pib_latent_attention(const float * q, const float * qlat, const pib_hlayer & L, const pib_hbatch & b, const float2 * rope, int rope_n_pos,
+                         const float * cache, int cache_row, const int32_t * cellmap, int n_ctx, float * ctx, cudaStream_t st);
+int pib_hgrn2_gates(float * qfv, int ld, const float * f_bias, const float * lower, int T, int HD, cudaStream_t st);
+int pib_hgrn2_scan(const float * qfv, int ld, const pib_hlayer & L, const pib_hbatch & b, float * state, size_t state_stride, const float * onorm, float eps,
+                   float * out, cudaStream_t st);
+int pib_polynorm(float * z, int T, int F, const float * act4, float eps, cudaStream_t st);
+int pib_moe_route(const float * logits, int T, int E, int top, int32_t * ids, float * wts, cudaStream_t st);
+int pib_moe_sort(const int32_t * ids, int n_pairs, int E, int32_t * counts, int32_t * offs, int32_t * perm, int32_t * inv, cudaStream_t st);
+int pib_moe_combine(const float * shared, const float * edn, const float * wts, const int32_t * inv, int T, int top, int W, float * y, cudaStream_t st);
+int pib_cellmap_set(int32_t * cellmap, int n_ctx, const pib_hbatch & b, cudaStream_t st);

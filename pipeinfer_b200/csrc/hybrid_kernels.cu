@@ -1,0 +1,484 @@
+// hybrid_kernels.cu -- the per-token and per-sequence kernels of layer-list models (hybrid.cuh).  Everything here computes in fp32:
+// norms, rotations, attention scores and weights, gates and the recurrence, the router.
+//
+//   LayerNorm (weight, no bias) on a sublayer's output, added to the residual stream
+//   causal convolution over time in front of a mixer, its last taps-1 inputs kept per sequence
+//   latent attention: per token one cached row [c | k_rot]; queries are folded through W_uk ("absorbed"), so a score is
+//       (q_lat . c + q_rot . k_rot) * scale, softmax over a sliding window plus one learned sink logit per head, and the
+//       output is sum_j p_j c_j (folded through W_uv by the caller)
+//   HGRN2: S_t = diag(f_t) S_{t-1} + (1 - f_t) v_t^T, o_t = S_t^T q_t, per head, state in fp32 per sequence
+//   PolyNorm, mixture-of-experts routing (softmax, top-k, renormalise), grouping of (token, expert) pairs by expert
+#include "hybrid.cuh"
+
+#include <cuda_bf16.h>
+
+#define CKL() do { cudaError_t e__ = cudaGetLastError(); if (e__ != cudaSuccess) { pib_set_error("%s:%d: launch failed: %s", __FILE__, __LINE__, cudaGetErrorString(e__)); return PIB_ERR_CUDA; } } while (0)
+
+// sum over the block (any block size that is a multiple of 32, up to 1024); every thread gets the result
+__device__ __forceinline__ float block_sum(float v, float * red) {
+    v = warp_sum(v);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = 0.f;
+    for (int i = 0; i < nw; i++) t += red[i];
+    return t;
+}
+
+// ---- LayerNorm ---------------------------------------------------------------------------------------------------------------
+// out[t] (+)= (in[t] - mean) / sqrt(mean((in[t] - mean)^2) + eps) * w     one block per token, the row staged in shared memory
+__device__ __forceinline__ void ln_row(const float * row, const float * __restrict__ w, float eps, int W, float * __restrict__ out, bool accumulate, float * red) {
+    float s = 0.f;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) s += row[i];
+    const float mean = block_sum(s, red) / W;
+    float q = 0.f;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) { const float d = row[i] - mean; q += d * d; }
+    const float inv = 1.0f / sqrtf(block_sum(q, red) / W + eps);
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        const float v = (row[i] - mean) * inv * w[i];
+        out[i] = accumulate ? out[i] + v : v;
+    }
+}
+
+__global__ void __launch_bounds__(256) layer_norm_kernel(const float * __restrict__ in, const float * __restrict__ w, float eps, int W, float * out, int accumulate) {
+    extern __shared__ float srow[];
+    __shared__ float red[32];
+    const float * r = in + (size_t) blockIdx.x * W;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) srow[i] = r[i];
+    __syncthreads();
+    ln_row(srow, w, eps, W, out + (size_t) blockIdx.x * W, accumulate != 0, red);
+}
+
+template <typename WT>
+__global__ void __launch_bounds__(256) embed_ln_kernel(const WT * __restrict__ embd, const int32_t * __restrict__ tok, const float * __restrict__ w, float eps, int W,
+                                                       float * __restrict__ x) {
+    extern __shared__ float srow[];
+    __shared__ float red[32];
+    const WT * r = embd + (size_t) tok[blockIdx.x] * W;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) srow[i] = (float) r[i];
+    __syncthreads();
+    ln_row(srow, w, eps, W, x + (size_t) blockIdx.x * W, false, red);
+}
+
+int pib_embed_ln(const pib_weight * embd, const int32_t * tok, const float * w, float eps, int T, int W, float * x, cudaStream_t st) {
+    if (embd->type == PIB_TYPE_BF16) embed_ln_kernel<__nv_bfloat16><<<T, 256, (size_t) W * 4, st>>>((const __nv_bfloat16 *) embd->base, tok, w, eps, W, x);
+    else                             embed_ln_kernel<float><<<T, 256, (size_t) W * 4, st>>>((const float *) embd->base, tok, w, eps, W, x);
+    CKL();
+    return PIB_OK;
+}
+
+int pib_layer_norm(const float * in, const float * w, float eps, int T, int W, float * out, int accumulate, cudaStream_t st) {
+    layer_norm_kernel<<<T, 256, (size_t) W * 4, st>>>(in, w, eps, W, out, accumulate);
+    CKL();
+    return PIB_OK;
+}
+
+// ---- causal convolution with a per-sequence tail ---------------------------------------------------------------------------------
+// h[t] = x[t] + sum_j w[:, j] * in(t - taps + 1 + j); in() is this batch's x inside the token's segment, the slot's tail before it
+#define CANON_MAX_TAPS 16
+__global__ void __launch_bounds__(256) canon_kernel(const float * __restrict__ x, const float * __restrict__ w, int taps, const int32_t * __restrict__ seg,
+                                                    const int32_t * __restrict__ seg_start, const int32_t * __restrict__ seg_slot,
+                                                    const float * __restrict__ state, size_t state_stride, size_t tail_off, int W, float * __restrict__ h) {
+    const int t = blockIdx.x, sg = seg[t], s0 = seg_start[sg];
+    const float * tail = state + (size_t) seg_slot[sg] * state_stride + tail_off;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        float acc = x[(size_t) t * W + c];
+        for (int j = 0; j < taps; j++) {
+            const int tau = t - (taps - 1) + j;
+            const float v = tau >= s0 ? x[(size_t) tau * W + c] : tail[(size_t) (taps - 1 + tau - s0) * W + c];
+            acc = fmaf(w[(size_t) c * taps + j], v, acc);
+        }
+        h[(size_t) t * W + c] = acc;
+    }
+}
+
+// after canon_kernel: the last taps-1 inputs of every segment become its slot's tail (old tail rows move up when the segment is shorter)
+__global__ void __launch_bounds__(256) canon_tail_kernel(const float * __restrict__ x, int taps, const int32_t * __restrict__ seg_start, const int32_t * __restrict__ seg_len,
+                                                         const int32_t * __restrict__ seg_slot, float * __restrict__ state, size_t state_stride, size_t tail_off, int W) {
+    const int sg = blockIdx.x, s0 = seg_start[sg], s1 = s0 + seg_len[sg];
+    float * tail = state + (size_t) seg_slot[sg] * state_stride + tail_off;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        float v[CANON_MAX_TAPS];
+#pragma unroll
+        for (int k = 0; k < CANON_MAX_TAPS; k++) {
+            if (k < taps - 1) {
+                const int tau = s1 - (taps - 1) + k;
+                v[k] = tau >= s0 ? x[(size_t) tau * W + c] : tail[(size_t) (taps - 1 + tau - s0) * W + c];
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < CANON_MAX_TAPS; k++) if (k < taps - 1) tail[(size_t) k * W + c] = v[k];
+    }
+}
+
+int pib_canon_conv(const float * x, const float * w, int taps, const pib_hbatch & b, float * state, size_t state_stride, size_t tail_off, int W, float * h,
+                   cudaStream_t st) {
+    if (taps > CANON_MAX_TAPS) { pib_set_error("convolution: %d taps (max %d)", taps, CANON_MAX_TAPS); return PIB_ERR_UNSUPP; }
+    canon_kernel<<<b.T, 256, 0, st>>>(x, w, taps, b.seg, b.seg_start, b.seg_slot, state, state_stride, tail_off, W, h);
+    CKL();
+    if (taps > 1) { canon_tail_kernel<<<b.S, 256, 0, st>>>(x, taps, b.seg_start, b.seg_len, b.seg_slot, state, state_stride, tail_off, W); CKL(); }
+    return PIB_OK;
+}
+
+// ---- position -> cell table of each state slot -----------------------------------------------------------------------------------
+__global__ void cellmap_kernel(int32_t * __restrict__ cellmap, int n_ctx, const int32_t * __restrict__ pos, const int32_t * __restrict__ cell,
+                               const int32_t * __restrict__ slot, int T) {
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t < T) cellmap[(size_t) slot[t] * n_ctx + pos[t]] = cell[t];
+}
+int pib_cellmap_set(int32_t * cellmap, int n_ctx, const pib_hbatch & b, cudaStream_t st) {
+    cellmap_kernel<<<(b.T + 255) / 256, 256, 0, st>>>(cellmap, n_ctx, b.pos, b.cell, b.slot, b.T);
+    CKL();
+    return PIB_OK;
+}
+
+// ---- latent attention: norms of the two latents, rotation of the shared key part, cache write --------------------------------------
+// proj[t] = [W_dq h (q_rank) | W_dkv h (kv_rank + rot_dim)]; cq[t] = RMSnorm(first part) * dq_norm; with a cache of its own the layer
+// writes cache[cell[t]] = [RMSnorm(next kv_rank) * dkv_norm | rotate(last rot_dim, pos[t])]
+__global__ void __launch_bounds__(128) latent_prep_kernel(const float * __restrict__ proj, int ldp, int q_rank, int kv_rank, int rot_dim, int rot_dims,
+                                                          const float * __restrict__ dq_norm, const float * __restrict__ dkv_norm, float eps,
+                                                          const int32_t * __restrict__ pos, const int32_t * __restrict__ cell,
+                                                          const float2 * __restrict__ rope, float * __restrict__ cq, float * __restrict__ cache, int cache_row) {
+    __shared__ float red[32];
+    const int     t = blockIdx.x;
+    const float * p = proj + (size_t) t * ldp;
+    float s = 0.f;
+    for (int i = threadIdx.x; i < q_rank; i += blockDim.x) s += p[i] * p[i];
+    const float rq = 1.0f / sqrtf(block_sum(s, red) / q_rank + eps);
+    for (int i = threadIdx.x; i < q_rank; i += blockDim.x) cq[(size_t) t * q_rank + i] = p[i] * rq * dq_norm[i];
+    if (!cache) return;
+    const float * d = p + q_rank;
+    s = 0.f;
+    for (int i = threadIdx.x; i < kv_rank; i += blockDim.x) s += d[i] * d[i];
+    const float rc = 1.0f / sqrtf(block_sum(s, red) / kv_rank + eps);
+    float * row = cache + (size_t) cell[t] * cache_row;
+    for (int i = threadIdx.x; i < kv_rank; i += blockDim.x) row[i] = d[i] * rc * dkv_norm[i];
+    const float *  k = d + kv_rank;
+    const int      half = rot_dims / 2;
+    const float2 * cs = rope + (size_t) pos[t] * half;
+    for (int i = threadIdx.x; i < rot_dim; i += blockDim.x) {
+        float v;
+        if (i < half)          v = k[i] * cs[i].x - k[i + half] * cs[i].y;
+        else if (i < rot_dims) v = k[i] * cs[i - half].x + k[i - half] * cs[i - half].y;
+        else                   v = k[i];
+        row[kv_rank + i] = v;
+    }
+}
+
+int pib_latent_prep(const float * proj, int ldp, const pib_hlayer & L, const float * dq_norm, const float * dkv_norm, float eps, const pib_hbatch & b,
+                    const float2 * rope, int rope_n_pos, float * cq, float * cache, int cache_row, cudaStream_t st) {
+    (void) rope_n_pos;
+    latent_prep_kernel<<<b.T, 128, 0, st>>>(proj, ldp, L.q_rank, L.kv_rank, L.rot_dim, L.rot_dims, dq_norm, dkv_norm, eps, b.pos, b.cell, rope, cq, cache, cache_row);
+    CKL();
+    return PIB_OK;
+}
+
+// ---- latent attention proper ---------------------------------------------------------------------------------------------------
+// grid (token, head group); a block holds HPB heads x KS key shares, one warp each.  A warp walks its share of the window
+// [max(0, p - window + 1), p], keeps a running maximum / denominator / weighted sum of latent rows (RPL registers per lane), and the
+// shares of a head are merged in shared memory.  The sink enters as one more logit with no row: the running state starts at
+// (max = sink, denominator = 1, sum = 0).
+template <int RPL>
+__global__ void __launch_bounds__(512) latent_attn_kernel(const float * __restrict__ q, int ldq, const float * __restrict__ qlat, int H, int D, int rot_dim, int rot_dims, int R,
+                                                          float scale, int window, const float * __restrict__ sink, const int32_t * __restrict__ pos,
+                                                          const int32_t * __restrict__ slot, const float2 * __restrict__ rope, const float * __restrict__ cache,
+                                                          int cache_row, const int32_t * __restrict__ cellmap, int n_ctx, int HPB, int KS, float * __restrict__ ctx) {
+    extern __shared__ float sm[];                 // [HPB * KS][R + 2] partial states, then [HPB][rot_dim] rotated queries
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int hl = warp / KS, ks = warp % KS, h = blockIdx.y * HPB + hl;
+    const int p = pos[t], lo = max(0, p - window + 1);
+    float * qr_s = sm + (size_t) HPB * KS * (R + 2) + (size_t) hl * rot_dim;
+    const bool live = h < H;
+    if (live && ks == 0) {
+        const float *  qr = q + (size_t) t * ldq + (size_t) h * (D + rot_dim) + D;
+        const int      half = rot_dims / 2;
+        const float2 * cs = rope + (size_t) p * half;
+        for (int i = lane; i < rot_dim; i += 32) {
+            float v;
+            if (i < half)          v = qr[i] * cs[i].x - qr[i + half] * cs[i].y;
+            else if (i < rot_dims) v = qr[i] * cs[i - half].x + qr[i - half] * cs[i - half].y;
+            else                   v = qr[i];
+            qr_s[i] = v;
+        }
+    }
+    __syncthreads();
+    float ql[RPL], acc[RPL];
+    float m = -INFINITY, l = 0.f;
+    if (live) {
+        const float * qlp = qlat + ((size_t) t * H + h) * R;
+#pragma unroll
+        for (int i = 0; i < RPL; i++) { const int r = i * 32 + lane; ql[i] = r < R ? qlp[r] : 0.f; acc[i] = 0.f; }
+        if (ks == 0) { m = sink[h]; l = 1.f; }
+        const int32_t * map = cellmap + (size_t) slot[t] * n_ctx;
+        for (int j = lo + ks; j <= p; j += KS) {
+            const float * row = cache + (size_t) map[j] * cache_row;
+            float c[RPL], s = 0.f;
+#pragma unroll
+            for (int i = 0; i < RPL; i++) { const int r = i * 32 + lane; c[i] = r < R ? row[r] : 0.f; s = fmaf(ql[i], c[i], s); }
+            for (int i = lane; i < rot_dim; i += 32) s = fmaf(qr_s[i], row[R + i], s);
+            s = warp_sum(s) * scale;
+            const float mn = fmaxf(m, s), a = expf(m - mn), e = expf(s - mn);         // m == -inf only before the first key: a = 0
+            l = l * a + e;
+#pragma unroll
+            for (int i = 0; i < RPL; i++) acc[i] = fmaf(acc[i], a, e * c[i]);
+            m = mn;
+        }
+        float * part = sm + (size_t) warp * (R + 2);
+#pragma unroll
+        for (int i = 0; i < RPL; i++) { const int r = i * 32 + lane; if (r < R) part[r] = acc[i]; }
+        if (lane == 0) { part[R] = m; part[R + 1] = l; }
+    }
+    __syncthreads();
+    if (live && ks == 0) {
+        const float * base = sm + (size_t) (hl * KS) * (R + 2);
+        float M = -INFINITY;
+        for (int k = 0; k < KS; k++) M = fmaxf(M, base[(size_t) k * (R + 2) + R]);
+        float Lsum = 0.f, o[RPL];
+#pragma unroll
+        for (int i = 0; i < RPL; i++) o[i] = 0.f;
+        for (int k = 0; k < KS; k++) {
+            const float * pk = base + (size_t) k * (R + 2);
+            const float   mk = pk[R];
+            if (mk == -INFINITY) continue;           // a share that saw no key
+            const float f = expf(mk - M);
+            Lsum = fmaf(pk[R + 1], f, Lsum);
+#pragma unroll
+            for (int i = 0; i < RPL; i++) { const int r = i * 32 + lane; if (r < R) o[i] = fmaf(pk[r], f, o[i]); }
+        }
+        const float inv = 1.0f / Lsum;
+        float * out = ctx + ((size_t) t * H + h) * R;
+#pragma unroll
+        for (int i = 0; i < RPL; i++) { const int r = i * 32 + lane; if (r < R) out[r] = o[i] * inv; }
+    }
+}
+
+int pib_latent_attention(const float * q, const float * qlat, const pib_hlayer & L, const pib_hbatch & b, const float2 * rope, int rope_n_pos,
+                         const float * cache, int cache_row, const int32_t * cellmap, int n_ctx, float * ctx, cudaStream_t st) {
+    (void) rope_n_pos;
+    const int H = L.heads, R = L.kv_rank;
+    const int HPB = H < 4 ? H : 4;
+    int KS = 16 / HPB;
+    if (L.window < 64) KS = 1;
+    while (KS > 1 && (size_t) HPB * KS * (R + 2) * 4 > 160 * 1024) KS >>= 1;
+    const size_t smem = ((size_t) HPB * KS * (R + 2) + (size_t) HPB * L.rot_dim) * 4;
+    dim3 grid((unsigned) b.T, (unsigned) ((H + HPB - 1) / HPB));
+    const int threads = HPB * KS * 32;
+#define LA_GO(RPL) do {                                                                                                            \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(latent_attn_kernel<RPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem); \
+        latent_attn_kernel<RPL><<<grid, threads, smem, st>>>(q, H * (L.dim + L.rot_dim), qlat, H, L.dim, L.rot_dim, L.rot_dims, R, L.scale, L.window, L.sink, b.pos,  \
+                                                             b.slot, rope, cache, cache_row, cellmap, n_ctx, HPB, KS, ctx);       \
+    } while (0)
+    if (R <= 128) LA_GO(4); else if (R <= 256) LA_GO(8); else if (R <= 512) LA_GO(16);
+    else { pib_set_error("latent attention: kv_rank %d (max 512)", R); return PIB_ERR_UNSUPP; }
+#undef LA_GO
+    CKL();
+    return PIB_OK;
+}
+
+// ---- HGRN2 ----------------------------------------------------------------------------------------------------------------------
+// in place on the projection rows [q | f | v]: q <- silu(q), f <- lower + (1 - lower) * sigmoid(f + bias)
+__global__ void hgrn2_gate_kernel(float * __restrict__ qfv, int ld, const float * __restrict__ f_bias, const float * __restrict__ lower, int T, int HD) {
+    const int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (int64_t) T * HD) return;
+    const int t = (int) (i / HD), c = (int) (i % HD);
+    float *   r = qfv + (size_t) t * ld;
+    const float qv = r[c];
+    r[c] = qv / (1.0f + expf(-qv));
+    const float lo = lower[c], g = 1.0f / (1.0f + expf(-(r[HD + c] + f_bias[c])));
+    r[HD + c] = lo + (1.0f - lo) * g;
+}
+int pib_hgrn2_gates(float * qfv, int ld, const float * f_bias, const float * lower, int T, int HD, cudaStream_t st) {
+    const int64_t n = (int64_t) T * HD;
+    hgrn2_gate_kernel<<<(unsigned) ((n + 255) / 256), 256, 0, st>>>(qfv, ld, f_bias, lower, T, HD);
+    CKL();
+    return PIB_OK;
+}
+
+// grid (segment, head), 4 * vdim threads: thread (vd, part) keeps rows d = part + 4 r of column vd of the head's matrix in registers,
+// walks the segment's tokens in order and leaves the matrix in the slot.  The four parts of a column sit in neighbouring lanes.
+template <int ROWS>
+__global__ void __launch_bounds__(512) hgrn2_scan_kernel(const float * __restrict__ qfv, int ld, int H, int D, int V, const int32_t * __restrict__ seg_start,
+                                                          const int32_t * __restrict__ seg_len, const int32_t * __restrict__ seg_slot, float * __restrict__ state,
+                                                          size_t state_stride, size_t state_off, float * __restrict__ out) {
+    const int sg = blockIdx.x, h = blockIdx.y, part = threadIdx.x & 3, vd = threadIdx.x >> 2;
+    const int s0 = seg_start[sg], n = seg_len[sg];
+    float *   S = state + (size_t) seg_slot[sg] * state_stride + state_off + (size_t) h * D * V;
+    float s[ROWS];
+#pragma unroll
+    for (int r = 0; r < ROWS; r++) { const int d = part + 4 * r; s[r] = d < D ? S[(size_t) d * V + vd] : 0.f; }
+    const int HD = H * D;
+    for (int i = 0; i < n; i++) {
+        const float * row = qfv + (size_t) (s0 + i) * ld;
+        const float * qp = row + (size_t) h * D, * fp = row + HD + (size_t) h * D;
+        const float   v = row[2 * HD + (size_t) h * V + vd];
+        float acc = 0.f;
+#pragma unroll
+        for (int r = 0; r < ROWS; r++) {
+            const int d = part + 4 * r;
+            if (d < D) {
+                const float f = fp[d];
+                s[r] = fmaf(f, s[r], (1.0f - f) * v);
+                acc = fmaf(qp[d], s[r], acc);
+            }
+        }
+        acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+        if (part == 0) out[(size_t) (s0 + i) * H * V + (size_t) h * V + vd] = acc;
+    }
+#pragma unroll
+    for (int r = 0; r < ROWS; r++) { const int d = part + 4 * r; if (d < D) S[(size_t) d * V + vd] = s[r]; }
+}
+
+// one warp per (token, head): o <- o / sqrt(mean(o^2) + eps) * w
+__global__ void head_rmsnorm_kernel(float * __restrict__ o, int n_rows, int V, const float * __restrict__ w, float eps) {
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= n_rows) return;
+    float * r = o + (size_t) row * V;
+    float s = 0.f;
+    for (int i = lane; i < V; i += 32) s += r[i] * r[i];
+    const float inv = 1.0f / sqrtf(warp_sum(s) / V + eps);
+    for (int i = lane; i < V; i += 32) r[i] = r[i] * inv * w[i];
+}
+
+int pib_hgrn2_scan(const float * qfv, int ld, const pib_hlayer & L, const pib_hbatch & b, float * state, size_t state_stride, const float * onorm, float eps,
+                   float * out, cudaStream_t st) {
+    const int H = L.heads, D = L.dim, V = L.vdim;
+    if (V * 4 > 512 || (V * 4) % 32 != 0 || D > 256) { pib_set_error("hgrn2: dim %d / vdim %d not supported (vdim a multiple of 8 up to 128, dim up to 256)", D, V); return PIB_ERR_UNSUPP; }
+    dim3 grid((unsigned) b.S, (unsigned) H);
+    const int rows = (D + 3) / 4;
+    if (rows <= 16)      hgrn2_scan_kernel<16><<<grid, V * 4, 0, st>>>(qfv, ld, H, D, V, b.seg_start, b.seg_len, b.seg_slot, state, state_stride, L.state_off, out);
+    else if (rows <= 32) hgrn2_scan_kernel<32><<<grid, V * 4, 0, st>>>(qfv, ld, H, D, V, b.seg_start, b.seg_len, b.seg_slot, state, state_stride, L.state_off, out);
+    else                 hgrn2_scan_kernel<64><<<grid, V * 4, 0, st>>>(qfv, ld, H, D, V, b.seg_start, b.seg_len, b.seg_slot, state, state_stride, L.state_off, out);
+    CKL();
+    const int n_rows = b.T * H;
+    head_rmsnorm_kernel<<<(n_rows + 7) / 8, 256, 0, st>>>(out, n_rows, V, onorm, eps);
+    CKL();
+    return PIB_OK;
+}
+
+// ---- PolyNorm: z <- a N(z) + b N(z^2) + c N(z^3) + e, N(u) = u / sqrt(mean(u^2) + eps) over the token's row ---------------------------
+__global__ void __launch_bounds__(256) polynorm_kernel(float * __restrict__ z, int F, float a, float b, float c, float e, float eps) {
+    __shared__ float red[32];
+    float * r = z + (size_t) blockIdx.x * F;
+    float s2 = 0.f, s4 = 0.f, s6 = 0.f;
+    for (int i = threadIdx.x; i < F; i += blockDim.x) { const float v = r[i], v2 = v * v; s2 += v2; s4 += v2 * v2; s6 += v2 * v2 * v2; }
+    const float n1 = a / sqrtf(block_sum(s2, red) / F + eps);
+    const float n2 = b / sqrtf(block_sum(s4, red) / F + eps);
+    const float n3 = c / sqrtf(block_sum(s6, red) / F + eps);
+    for (int i = threadIdx.x; i < F; i += blockDim.x) { const float v = r[i]; r[i] = fmaf(v, n1, fmaf(v * v, n2, fmaf(v * v * v, n3, e))); }
+}
+int pib_polynorm(float * z, int T, int F, const float * act4, float eps, cudaStream_t st) {
+    polynorm_kernel<<<T, 256, 0, st>>>(z, F, act4[0], act4[1], act4[2], act4[3], eps);
+    CKL();
+    return PIB_OK;
+}
+
+// ---- mixture of experts ------------------------------------------------------------------------------------------------------------
+// one warp per token: softmax over the E router logits, the `top` largest scores (ties: the lower index), weights = score / (sum of the chosen + 1e-20)
+#define MOE_MAX_TOP 16
+__global__ void moe_route_kernel(const float * __restrict__ logits, int T, int E, int top, int32_t * __restrict__ ids, float * __restrict__ wts) {
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (t >= T) return;
+    const float * z = logits + (size_t) t * E;
+    float mx = -INFINITY;
+    for (int i = lane; i < E; i += 32) mx = fmaxf(mx, z[i]);
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int i = lane; i < E; i += 32) sum += expf(z[i] - mx);
+    sum = warp_sum(sum);
+    int   chosen[MOE_MAX_TOP];
+    float score[MOE_MAX_TOP], tot = 0.f;
+    for (int k = 0; k < top; k++) {
+        float bv = -INFINITY;
+        int   bi = 0x7fffffff;
+        for (int i = lane; i < E; i += 32) {
+            bool taken = false;
+            for (int j = 0; j < k; j++) taken |= chosen[j] == i;
+            const float v = z[i];
+            if (!taken && (v > bv || (v == bv && i < bi))) { bv = v; bi = i; }
+        }
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int   oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        chosen[k] = bi;
+        score[k]  = expf(bv - mx) / sum;
+        tot += score[k];
+    }
+    if (lane == 0)
+        for (int k = 0; k < top; k++) { ids[(size_t) t * top + k] = chosen[k]; wts[(size_t) t * top + k] = score[k] / (tot + 1e-20f); }
+}
+int pib_moe_route(const float * logits, int T, int E, int top, int32_t * ids, float * wts, cudaStream_t st) {
+    if (top > MOE_MAX_TOP || top > E) { pib_set_error("router: top %d of %d experts (max %d)", top, E, MOE_MAX_TOP); return PIB_ERR_UNSUPP; }
+    moe_route_kernel<<<(T + 7) / 8, 256, 0, st>>>(logits, T, E, top, ids, wts);
+    CKL();
+    return PIB_OK;
+}
+
+// pairs (token, k) grouped by expert, inside an expert in pair order: counts[e]; offs[e] = first sorted position of expert e;
+// perm[sorted position] = pair; inv[pair] = sorted position.  No atomics: the order, and so every sum formed from it, is fixed.
+__global__ void __launch_bounds__(256) moe_count_kernel(const int32_t * __restrict__ ids, int n_pairs, int32_t * __restrict__ counts) {
+    __shared__ float red[32];
+    const int e = blockIdx.x;
+    int n = 0;
+    for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) n += ids[i] == e;
+    const float tot = block_sum((float) n, red);          // exact below 2^24 pairs
+    if (threadIdx.x == 0) counts[e] = (int32_t) tot;
+}
+__global__ void __launch_bounds__(256) moe_fill_kernel(const int32_t * __restrict__ ids, int n_pairs, int E, const int32_t * __restrict__ counts,
+                                                       int32_t * __restrict__ offs, int32_t * __restrict__ perm, int32_t * __restrict__ inv) {
+    __shared__ int wsum[8];
+    __shared__ int base_s;
+    const int e = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x == 0) {
+        int o = 0;
+        for (int i = 0; i < e; i++) o += counts[i];
+        base_s = o;
+        offs[e] = o;
+        if (e == E - 1) offs[E] = o + counts[e];
+    }
+    __syncthreads();
+    int base = base_s;
+    for (int i0 = 0; i0 < n_pairs; i0 += 256) {
+        const int  i = i0 + threadIdx.x;
+        const bool mine = i < n_pairs && ids[i] == e;
+        const unsigned bal = __ballot_sync(0xffffffffu, mine);
+        if (lane == 0) wsum[warp] = __popc(bal);
+        __syncthreads();
+        int before = 0, total = 0;
+        for (int w = 0; w < 8; w++) { if (w < warp) before += wsum[w]; total += wsum[w]; }
+        if (mine) {
+            const int p = base + before + __popc(bal & ((1u << lane) - 1u));
+            perm[p] = i;
+            inv[i]  = p;
+        }
+        base += total;
+        __syncthreads();
+    }
+}
+int pib_moe_sort(const int32_t * ids, int n_pairs, int E, int32_t * counts, int32_t * offs, int32_t * perm, int32_t * inv, cudaStream_t st) {
+    if (n_pairs >= (1 << 24)) { pib_set_error("router: %d pairs in one batch", n_pairs); return PIB_ERR_UNSUPP; }
+    moe_count_kernel<<<E, 256, 0, st>>>(ids, n_pairs, counts);
+    CKL();
+    moe_fill_kernel<<<E, 256, 0, st>>>(ids, n_pairs, E, counts, offs, perm, inv);
+    CKL();
+    return PIB_OK;
+}
+
+// y[t] = shared[t] + sum_k w[t][k] * edn[inv[t * top + k]]   (k in ascending order)
+__global__ void moe_combine_kernel(const float * __restrict__ shared, const float * __restrict__ edn, const float * __restrict__ wts, const int32_t * __restrict__ inv,
+                                   int top, int W, float * __restrict__ y) {
+    const int t = blockIdx.x;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        float acc = shared ? shared[(size_t) t * W + c] : 0.f;
+        for (int k = 0; k < top; k++) acc = fmaf(wts[(size_t) t * top + k], edn[(size_t) inv[(size_t) t * top + k] * W + c], acc);
+        y[(size_t) t * W + c] = acc;
+    }
+}
+int pib_moe_combine(const float * shared, const float * edn, const float * wts, const int32_t * inv, int T, int top, int W, float * y, cudaStream_t st) {
+    moe_combine_kernel<<<T, 256, 0, st>>>(shared, edn, wts, inv, top, W, y);
+    CKL();
+    return PIB_OK;
+}

@@ -164,6 +164,48 @@ bool KvMirror::find_slot(int n_tokens_i, const int32_t * tpos, const uint32_t * 
 }
 
 // host replay of one device-level op-log record (what kv_apply_kernel does on the replica)
+bool KvMirror::find_cells(int n_tokens, const int32_t * tpos, const uint32_t * tokbits, int32_t * cells_out) {
+    if (n_tokens < 0 || used + (uint32_t) n_tokens > size) return false;
+    uint32_t c = head < size ? head : 0;
+    int got = 0;
+    for (uint32_t tested = 0; tested < size && got < n_tokens; tested++, c = c + 1 < size ? c + 1 : 0)
+        if (pos[c] < 0) cells_out[got++] = (int32_t) c;
+    if (got < n_tokens) return false;
+    for (int i = 0; i < n_tokens; i++) {
+        const uint32_t cell = (uint32_t) cells_out[i];
+        pos[cell] = tpos[i];
+        uint32_t *       r = &bits[(size_t) cell * n_words];
+        const uint32_t * t = tokbits + (size_t) i * n_words;
+        for (int w = 0; w < n_words; w++) r[w] |= t[w];
+    }
+    used += (uint32_t) n_tokens;
+    head = (uint32_t) cells_out[n_tokens - 1] + 1 < size ? (uint32_t) cells_out[n_tokens - 1] + 1 : 0;
+    return true;
+}
+
+bool SeqSlots::apply(const KvOp & op) {
+    switch (op.op) {
+        case KVOP_CLEAR: for (int i = 0; i < n_slots(); i++) release_slot(i); return true;
+        case KVOP_KEEP:  for (int i = 0; i < n_slots(); i++) if (seq[(size_t) i] != op.a) release_slot(i); return true;
+        case KVOP_RM: {
+            bool ok = true;
+            for (int i = 0; i < n_slots(); i++) {
+                const int32_t s = seq[(size_t) i];
+                if (s < 0 || (op.a >= 0 && (s < op.a || s > (op.b > op.a ? op.b : op.a)))) continue;
+                const int32_t p0 = op.p0 < 0 ? 0 : op.p0, p1 = op.p1 < 0 ? INT32_MAX : op.p1;
+                if (p0 == 0 && p1 >= len[(size_t) i]) release_slot(i);
+                else if (p0 < len[(size_t) i] && p1 > p0) ok = false;         // cells inside the fed range go, the state cannot follow
+            }
+            return ok;
+        }
+        case KVOP_CP: case KVOP_SWEEP: {
+            for (int i = 0; i < n_slots(); i++) if (seq[(size_t) i] >= 0 && (seq[(size_t) i] == op.a || op.op == KVOP_SWEEP)) return false;
+            return true;
+        }
+        default: return true;
+    }
+}
+
 void KvMirror::apply(const KvOp & op, const int32_t * tpos, const uint32_t * tokbits) {
     switch (op.op) {
         case KVOP_CLEAR:   clear(); break;
@@ -514,4 +556,46 @@ extern "C" void pib_kvtest_state(void * h, int32_t * scalars3, int32_t * pos, ui
     scalars3[0] = (int32_t) t->kv.head; scalars3[1] = (int32_t) t->kv.used; scalars3[2] = (int32_t) t->kv.n;
     memcpy(pos, t->kv.pos.data(), sizeof(int32_t) * t->kv.size);
     memcpy(bits, t->kv.bits.data(), sizeof(uint32_t) * t->kv.bits.size());
+}
+
+// ---- CPU-only test hooks for the scattered cell allocator and the state slots (no CUDA call) ------------------------------------------
+struct pib_slottest { KvMirror kv; SeqSlots sl; };
+extern "C" void * pib_slottest_new(uint32_t n_ctx, int32_t max_seq, int n_slots) {
+    pib_slottest * t = new pib_slottest();
+    t->kv.init(n_ctx, max_seq);
+    t->sl.init(n_slots);
+    return t;
+}
+extern "C" void pib_slottest_free(void * h) { delete (pib_slottest *) h; }
+// a cache op on both the cells and the slots; -1 when the slots cannot follow it
+extern "C" int pib_slottest_op(void * h, int op, int a, int b, int p0, int p1) {
+    pib_slottest * t = (pib_slottest *) h;
+    KvOp o = { op, a, op == KVOP_RM && a >= 0 ? a : b, p0, p1, 0 };
+    const bool ok = t->sl.apply(o);
+    switch (op) {
+        case KVOP_CLEAR: t->kv.clear(); break;
+        case KVOP_RM:    t->kv.seq_rm(o.a, o.b, p0, p1); break;
+        case KVOP_KEEP:  t->kv.seq_keep(a); break;
+        default: break;
+    }
+    return ok ? 0 : -1;
+}
+// n tokens of one sequence at positions pos[]: slot (taken if the sequence has none) and cells; -1 no slot, -2 no cells
+extern "C" int pib_slottest_feed(void * h, int n, const int32_t * pos, int seq, int32_t * cells_out) {
+    pib_slottest * t = (pib_slottest *) h;
+    int slot = t->sl.find(seq);
+    if (slot < 0 && t->sl.n_free() == 0) return -1;
+    std::vector<uint32_t> tb((size_t) n * t->kv.n_words, 0u);
+    for (int i = 0; i < n; i++) tb[(size_t) i * t->kv.n_words + (seq >> 5)] |= 1u << (seq & 31);
+    if (!t->kv.find_cells(n, pos, tb.data(), cells_out)) return -2;
+    if (slot < 0) slot = t->sl.acquire(seq);
+    t->sl.len[(size_t) slot] += n;
+    return slot;
+}
+extern "C" void pib_slottest_state(void * h, int32_t * used, int32_t * cell_pos, int32_t * slot_seq, int32_t * slot_len) {
+    pib_slottest * t = (pib_slottest *) h;
+    *used = (int32_t) t->kv.used;
+    memcpy(cell_pos, t->kv.pos.data(), sizeof(int32_t) * t->kv.size);
+    memcpy(slot_seq, t->sl.seq.data(), sizeof(int32_t) * t->sl.seq.size());
+    memcpy(slot_len, t->sl.len.data(), sizeof(int32_t) * t->sl.len.size());
 }

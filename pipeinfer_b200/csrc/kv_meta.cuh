@@ -53,8 +53,28 @@ struct KvMirror {
     // find_slot: returns false when there is no run of n_tokens free cells; on success head points at the slot and the
     // cells are filled from pos / per-token bitset rows (tokbits: [n_tokens][n_words])
     bool    find_slot(int n_tokens, const int32_t * tpos, const uint32_t * tokbits);
+    // any n_tokens free cells, not necessarily neighbours (models whose kernels find a sequence's cells through a position ->
+    // cell table): scans from head, wraps once; cells_out[i] is the cell of token i.  False (nothing changed) when fewer are free.
+    bool    find_cells(int n_tokens, const int32_t * tpos, const uint32_t * tokbits, int32_t * cells_out);
     int32_t cell_max() const;
     void    apply(const KvOp & op, const int32_t * tpos, const uint32_t * tokbits);
+};
+
+// State slots: what a sequence of a recurrent / convolutional model keeps besides KV cells lives in one of n_slots fixed-size
+// device records.  A sequence takes a slot at its first token and gives it back when the whole sequence is removed from the
+// cache (seq_rm with an open range, clear, or seq_keep of another sequence); the next owner starts from a zeroed record.
+struct SeqSlots {
+    std::vector<int32_t> seq;       // [n_slots] owner (-1: free)
+    std::vector<int32_t> len;       // [n_slots] tokens the owner has fed
+    void init(int n_slots) { seq.assign((size_t) n_slots, -1); len.assign((size_t) n_slots, 0); }
+    int  n_slots() const { return (int) seq.size(); }
+    int  find(int32_t s) const { for (size_t i = 0; i < seq.size(); i++) if (seq[i] == s) return (int) i; return -1; }
+    int  n_free() const { int n = 0; for (int32_t s : seq) n += s < 0; return n; }
+    int  acquire(int32_t s) { for (size_t i = 0; i < seq.size(); i++) if (seq[i] < 0) { seq[i] = s; len[i] = 0; return (int) i; } return -1; }
+    void release_slot(int i) { seq[(size_t) i] = -1; len[(size_t) i] = 0; }
+    // the effect of a cache op on slot ownership; returns false for an op a recurrent state cannot follow (a partial removal
+    // inside the fed range, a copy between sequences)
+    bool apply(const KvOp & op);
 };
 
 // CPU-only test harness around the mirror and the op-log front end (kv_meta.cu; pipeline.cu for the replicated variant)

@@ -1,5 +1,7 @@
 // llama_api.cu -- the llama.h-compatible C ABI (include/pipeinfer_llama.h) on top of the engine.
 #include "engine.cuh"
+#include "hybrid.cuh"
+#include <sys/stat.h>
 #include "tokenizer.cuh"
 #include "../../include/pipeinfer_llama.h"
 
@@ -64,7 +66,41 @@ struct llama_context_params llama_context_default_params(void) {
 void llama_backend_init(bool numa) { (void) numa; ensure_init(); }
 void llama_backend_free(void) {}
 
+// a folder (config.json + model.safetensors) instead of a GGUF file; compute type from PIB_DTYPE ("float32": everything in true
+// 32-bit; default bfloat16 operands with fp32 accumulation)
+static bool is_model_dir(const char * path) {
+    struct stat sb;
+    if (stat(path, &sb) == 0 && S_ISDIR(sb.st_mode)) return true;
+    const size_t n = strlen(path);
+    return n > 12 && !strcmp(path + n - 12, "/config.json");
+}
+static int env_dtype() { const char * e = getenv("PIB_DTYPE"); return e && (!strcmp(e, "float32") || !strcmp(e, "f32")) ? PIB_TYPE_F32 : PIB_TYPE_BF16; }
+
+struct llama_model * llama_pib_load_model_dir(const char * path, int float32) {
+    ensure_init();
+    pib_model * m = pib_model_load_dir(path, float32 ? PIB_TYPE_F32 : PIB_TYPE_BF16);
+    if (!m) { fprintf(stderr, "llama_pib_load_model_dir: %s\n", pib_last_error()); return nullptr; }
+    llama_model * lm = new llama_model();
+    lm->m = m;
+    return lm;
+}
+
+// random weights for a configuration given as config.json text (benchmarks of layer-list designs at sizes no file exists for)
+struct llama_model * llama_pib_synthetic_config_model(const char * config_json, uint64_t seed, int float32) {
+    ensure_init();
+    pib_model * m = pib_hybrid_synthetic(config_json, seed, float32 ? PIB_TYPE_F32 : PIB_TYPE_BF16);
+    if (!m) { fprintf(stderr, "llama_pib_synthetic_config_model: %s\n", pib_last_error()); return nullptr; }
+    llama_model * lm = new llama_model();
+    lm->m = m;
+    return lm;
+}
+
+// state slots of a layer-list model's context (default: min(max_seq_ids, 8), or PIB_STATE_SLOTS); call before the first decode
+int llama_pib_set_state_slots(struct llama_context * ctx, int n_slots) { return pib_hybrid_set_slots(ctx->c, n_slots); }
+int llama_pib_state_slots_free(const struct llama_context * ctx) { return pib_hybrid_slots_free(ctx->c); }
+
 struct llama_model * llama_load_model_from_file(const char * path_model, struct llama_model_params params) {
+    if (is_model_dir(path_model)) return params.vocab_only ? nullptr : llama_pib_load_model_dir(path_model, env_dtype() == PIB_TYPE_F32);
     // vocab_only (llama.h:176): hyper-parameters and vocabulary, no tensor, no CUDA call -- the tokenizer works without a GPU
     if (!params.vocab_only) ensure_init();
     pib_model * m = params.vocab_only ? pib_model_load_gguf(path_model, 0, 0, false, false) : pib_model_load_gguf(path_model, 0, -1, true, true);

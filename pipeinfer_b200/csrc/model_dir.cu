@@ -1,0 +1,396 @@
+// model_dir.cu -- models that come as a folder: config.json (sizes, constants and the list of layers) + model.safetensors (weights).
+//
+// A safetensors file is an 8-byte little-endian length, that many bytes of JSON (tensor name -> dtype, shape, data_offsets) and
+// then the tensors' bytes.  config.json's "architecture" picks the builder from the registry below, as general.architecture does
+// for GGUF files (engine.cu).  Weights arrive as bfloat16; for a float32 context they are widened once at load (exactly).
+#include "hybrid.cuh"
+
+#include <cuda_bf16.h>
+#include <math.h>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <fcntl.h>
+#include <unistd.h>
+
+#include <algorithm>
+#include <memory>
+
+// ---- a small JSON reader ---------------------------------------------------------------------------------------------------------
+struct Json {
+    enum Kind { NUL, BOOL, NUM, STR, ARR, OBJ } kind = NUL;
+    double num = 0; bool b = false; std::string str;
+    std::vector<Json> arr;
+    std::vector<std::pair<std::string, Json>> obj;
+    const Json * get(const char * k) const { for (auto & kv : obj) if (kv.first == k) return &kv.second; return nullptr; }
+    bool is_null() const { return kind == NUL; }
+};
+struct JsonParser {
+    const char * p, * end; bool ok = true;
+    void ws() { while (p < end && (*p == ' ' || *p == '\n' || *p == '\t' || *p == '\r')) p++; }
+    bool lit(const char * s) { size_t n = strlen(s); if ((size_t) (end - p) >= n && !memcmp(p, s, n)) { p += n; return true; } return false; }
+    std::string string() {
+        std::string s;
+        if (p >= end || *p != '"') { ok = false; return s; }
+        p++;
+        while (p < end && *p != '"') {
+            if (*p == '\\' && p + 1 < end) {
+                p++;
+                switch (*p) {
+                    case 'n': s += '\n'; break; case 't': s += '\t'; break; case 'r': s += '\r'; break; case 'b': s += '\b'; break; case 'f': s += '\f'; break;
+                    case 'u': { unsigned cp = 0; for (int i = 0; i < 4 && p + 1 < end; i++) { p++; cp = cp * 16 + (unsigned) (isdigit((unsigned char) *p) ? *p - '0' : (tolower(*p) - 'a' + 10)); }
+                                if (cp < 0x80) s += (char) cp; else if (cp < 0x800) { s += (char) (0xC0 | (cp >> 6)); s += (char) (0x80 | (cp & 0x3F)); }
+                                else { s += (char) (0xE0 | (cp >> 12)); s += (char) (0x80 | ((cp >> 6) & 0x3F)); s += (char) (0x80 | (cp & 0x3F)); } break; }
+                    default: s += *p;
+                }
+                p++;
+            } else s += *p++;
+        }
+        if (p >= end) { ok = false; return s; }
+        p++;
+        return s;
+    }
+    Json value(int depth = 0) {
+        Json v;
+        ws();
+        if (p >= end || depth > 64) { ok = false; return v; }
+        if (*p == '{') {
+            v.kind = Json::OBJ; p++; ws();
+            if (p < end && *p == '}') { p++; return v; }
+            while (ok) {
+                ws();
+                std::string k = string();
+                ws();
+                if (p >= end || *p != ':') { ok = false; break; }
+                p++;
+                v.obj.emplace_back(k, value(depth + 1));
+                ws();
+                if (p < end && *p == ',') { p++; continue; }
+                if (p < end && *p == '}') { p++; break; }
+                ok = false;
+            }
+        } else if (*p == '[') {
+            v.kind = Json::ARR; p++; ws();
+            if (p < end && *p == ']') { p++; return v; }
+            while (ok) {
+                v.arr.push_back(value(depth + 1));
+                ws();
+                if (p < end && *p == ',') { p++; continue; }
+                if (p < end && *p == ']') { p++; break; }
+                ok = false;
+            }
+        } else if (*p == '"') { v.kind = Json::STR; v.str = string(); }
+        else if (lit("true")) { v.kind = Json::BOOL; v.b = true; }
+        else if (lit("false")) { v.kind = Json::BOOL; }
+        else if (lit("null")) {}
+        else {
+            char * e = nullptr;
+            std::string t(p, std::min<size_t>(64, (size_t) (end - p)));
+            v.num = strtod(t.c_str(), &e);
+            if (e == t.c_str()) { ok = false; return v; }
+            v.kind = Json::NUM; p += e - t.c_str();
+        }
+        return v;
+    }
+};
+static bool json_parse(const char * s, size_t n, Json & out) { JsonParser P{ s, s + n }; out = P.value(); P.ws(); return P.ok; }
+
+static bool read_file(const std::string & path, std::string & out) {
+    FILE * f = fopen(path.c_str(), "rb");
+    if (!f) return false;
+    fseek(f, 0, SEEK_END); long n = ftell(f); fseek(f, 0, SEEK_SET);
+    out.resize(n > 0 ? (size_t) n : 0);
+    const bool ok = n >= 0 && fread(&out[0], 1, out.size(), f) == out.size();
+    fclose(f);
+    return ok;
+}
+
+// ---- safetensors ------------------------------------------------------------------------------------------------------------------
+struct StTensor { std::string dtype; std::vector<int64_t> shape; const uint8_t * data = nullptr; size_t bytes = 0; int64_t numel() const { int64_t n = 1; for (auto d : shape) n *= d; return n; } };
+struct SafeTensors {
+    void * map = nullptr; size_t size = 0;
+    std::map<std::string, StTensor> t;
+    ~SafeTensors() { if (map) munmap(map, size); }
+    bool open(const std::string & path) {
+        const int fd = ::open(path.c_str(), O_RDONLY);
+        if (fd < 0) { pib_set_error("model: cannot open %s", path.c_str()); return false; }
+        struct stat sb;
+        if (fstat(fd, &sb) != 0 || sb.st_size < 8) { close(fd); pib_set_error("model: %s is too short", path.c_str()); return false; }
+        size = (size_t) sb.st_size;
+        map = mmap(nullptr, size, PROT_READ, MAP_PRIVATE, fd, 0);
+        close(fd);
+        if (map == MAP_FAILED) { map = nullptr; pib_set_error("model: mmap of %s failed", path.c_str()); return false; }
+        const uint8_t * b = (const uint8_t *) map;
+        uint64_t hl = 0;
+        for (int i = 7; i >= 0; i--) hl = (hl << 8) | b[i];
+        if (hl > size - 8) { pib_set_error("model: %s: header length %llu exceeds the file", path.c_str(), (unsigned long long) hl); return false; }
+        Json h;
+        if (!json_parse((const char *) b + 8, (size_t) hl, h) || h.kind != Json::OBJ) { pib_set_error("model: %s: header is not JSON", path.c_str()); return false; }
+        const uint8_t * data = b + 8 + hl;
+        const size_t    dsz  = size - 8 - (size_t) hl;
+        for (auto & kv : h.obj) {
+            if (kv.first == "__metadata__") continue;
+            const Json * dt = kv.second.get("dtype"), * sh = kv.second.get("shape"), * of = kv.second.get("data_offsets");
+            if (!dt || !sh || !of || of->arr.size() != 2) { pib_set_error("model: tensor %s: incomplete header entry", kv.first.c_str()); return false; }
+            StTensor x;
+            x.dtype = dt->str;
+            for (auto & d : sh->arr) x.shape.push_back((int64_t) d.num);
+            const size_t a = (size_t) of->arr[0].num, e = (size_t) of->arr[1].num;
+            if (e < a || e > dsz) { pib_set_error("model: tensor %s: data offsets outside the file", kv.first.c_str()); return false; }
+            x.data = data + a; x.bytes = e - a;
+            const size_t es = x.dtype == "BF16" || x.dtype == "F16" ? 2 : (x.dtype == "F32" || x.dtype == "I32") ? 4 : 0;
+            if (es == 0 || (size_t) x.numel() * es != x.bytes) { pib_set_error("model: tensor %s: dtype %s / shape do not fit %zu bytes", kv.first.c_str(), x.dtype.c_str(), x.bytes); return false; }
+            t[kv.first] = x;
+        }
+        return true;
+    }
+};
+
+// ---- tensor sources: a file, or a seeded generator (synthetic models of a configuration, for benchmarks) -----------------------------
+struct TensorSource {
+    SafeTensors * st = nullptr;
+    uint64_t      seed = 0;
+    bool          failed = false;
+    // the tensor as float32, shape checked
+    bool get(const std::string & name, std::initializer_list<int64_t> shape, std::vector<float> & out) {
+        int64_t n = 1;
+        for (auto d : shape) n *= d;
+        out.resize((size_t) n);
+        if (!st) { synth(name, shape, out); return true; }
+        auto it = st->t.find(name);
+        if (it == st->t.end()) { pib_set_error("model: tensor %s is missing", name.c_str()); failed = true; return false; }
+        const StTensor & x = it->second;
+        if (x.shape != std::vector<int64_t>(shape)) { pib_set_error("model: tensor %s has another shape than the configuration gives", name.c_str()); failed = true; return false; }
+        if (x.dtype == "BF16") { const uint16_t * s = (const uint16_t *) x.data; for (int64_t i = 0; i < n; i++) { uint32_t u = (uint32_t) s[i] << 16; memcpy(&out[i], &u, 4); } }
+        else if (x.dtype == "F32") memcpy(out.data(), x.data, (size_t) n * 4);
+        else if (x.dtype == "F16") { const __half * s = (const __half *) x.data; for (int64_t i = 0; i < n; i++) out[i] = __half2float(s[i]); }
+        else { pib_set_error("model: tensor %s: dtype %s", name.c_str(), x.dtype.c_str()); failed = true; return false; }
+        return true;
+    }
+    static bool ends(const std::string & s, const char * e) { const size_t n = strlen(e); return s.size() >= n && !s.compare(s.size() - n, n, e); }
+    void synth(const std::string & name, std::initializer_list<int64_t> shape, std::vector<float> & out) {
+        uint64_t h = seed * 0x9E3779B97F4A7C15ull + 0x1234567;
+        for (char ch : name) h = (h ^ (uint8_t) ch) * 0x100000001B3ull;
+        auto next = [&]() { h ^= h << 13; h ^= h >> 7; h ^= h << 17; return (float) ((h >> 11) & 0xFFFFFF) / 16777216.0f; };     // [0, 1)
+        const int64_t last = *(shape.end() - 1);
+        const bool norm = ends(name, "norm") || ends(name, "norm1") || ends(name, "norm2");
+        const float amp = 1.5f * sqrtf(3.0f / (float) last);
+        for (size_t i = 0; i < out.size(); i++) {
+            const float u = next() * 2.f - 1.f;
+            float v;
+            if (norm) v = 1.0f + 0.2f * u;
+            else if (ends(name, "lower")) v = 0.45f + 0.45f * u;
+            else if (ends(name, ".act")) v = (i == 0 ? 0.6f : i == 1 ? 0.3f : i == 2 ? 0.2f : 0.05f);
+            else if (ends(name, "sink") || ends(name, "f.b")) v = u;
+            else if (ends(name, "canon1")) v = 0.3f * u;
+            else if (name == "embed") v = 1.7f * u;
+            else v = amp * u;
+            out[i] = __bfloat162float(__float2bfloat16_rn(v));
+        }
+    }
+};
+
+static float * upload_f32v(const std::vector<float> & v) {
+    float * d = nullptr;
+    if (cudaMalloc(&d, std::max<size_t>(16, v.size() * 4)) != cudaSuccess || cudaMemcpy(d, v.data(), v.size() * 4, cudaMemcpyHostToDevice) != cudaSuccess) {
+        pib_set_error("model: upload of %zu floats failed: %s", v.size(), cudaGetErrorString(cudaGetLastError()));
+        return nullptr;
+    }
+    return d;
+}
+// a matrix for the dense matmul: bfloat16 rows in served mode, float32 rows in exact mode (dtype = PIB_TYPE_BF16 / PIB_TYPE_F32)
+static pib_weight * upload_mat(const std::vector<float> & v, int64_t N, int64_t K, int dtype, pib_model * m) {
+    pib_weight * w;
+    if (dtype == PIB_TYPE_F32) w = pib_dense_upload(PIB_TYPE_F32, v.data(), N, K);
+    else {
+        std::vector<__nv_bfloat16> hb(v.size());
+        for (size_t i = 0; i < v.size(); i++) hb[i] = __float2bfloat16_rn(v[i]);
+        w = pib_dense_upload(PIB_TYPE_BF16, hb.data(), N, K);
+    }
+    if (w) m->weight_bytes += w->bytes;
+    return w;
+}
+
+static double jnum(const Json * o, const char * k, double dflt, bool * ok = nullptr) {
+    const Json * v = o ? o->get(k) : nullptr;
+    if (!v || v->kind != Json::NUM) { if (ok) *ok = false; return dflt; }
+    return v->num;
+}
+
+// ---- the Rapisun builder ----------------------------------------------------------------------------------------------------------
+// Reads every size and constant from the configuration; tensor names are '<layer>.mix.*', '<layer>.mlp.*', '<layer>.norm1|norm2|canon1'.
+static pib_model * build_rapisun(const Json & cfg, TensorSource & src, int dtype) {
+    std::unique_ptr<pib_model, void (*)(pib_model *)> mp(new pib_model(), pib_model_free);
+    pib_model * m = mp.get();
+    pib_hybrid * hy = new pib_hybrid();
+    m->hy = hy;
+    m->arch = 2; m->name = "Rapisun";
+    bool ok = true;
+    const int W = (int) jnum(&cfg, "width", 0, &ok), V = (int) jnum(&cfg, "vocab", 0, &ok);
+    const Json * layers = cfg.get("layers");
+    if (!ok || W <= 0 || V <= 0 || !layers || layers->kind != Json::ARR) { pib_set_error("model: config.json needs width, vocab and layers"); return nullptr; }
+    hy->dtype = dtype;
+    hy->eps = (float) jnum(cfg.get("norm"), "eps", 1e-5);
+    hy->taps = cfg.get("canon") ? (int) jnum(cfg.get("canon"), "taps", 1) : 0;
+    m->n_embd = W; m->n_vocab = V; m->n_layer = (int) layers->arr.size(); m->layer_begin = 0; m->layer_end = m->n_layer;
+    m->wtype = dtype; m->n_ctx_train = 1 << 20; m->n_head = 1; m->n_head_kv = 1; m->tok_bos = -1; m->tok_eos = -1;
+    std::vector<float> v;
+#define GET(name, ...) do { if (!src.get((name), { __VA_ARGS__ }, v)) return nullptr; } while (0)
+#define VEC(dst, name, n) do { GET(name, (int64_t) (n)); if (!((dst) = upload_f32v(v))) return nullptr; } while (0)
+#define MAT(dst, name, N, K) do { GET(name, (int64_t) (N), (int64_t) (K)); if (!((dst) = upload_mat(v, (N), (K), dtype, m))) return nullptr; } while (0)
+    MAT(m->tok_embd, "embed", V, W);
+    VEC(hy->embd_norm, "embed.norm", W);
+    VEC(m->output_norm, "final.norm", W);
+    MAT(m->output, "head", V, W);
+    hy->layers.resize(m->n_layer);
+    size_t state = 0;
+    auto widen = [](int & a, int64_t b) { if (b > a) a = (int) b; };
+    for (int il = 0; il < m->n_layer; il++) {
+        const Json & jl = layers->arr[il];
+        pib_hlayer & L = hy->layers[il];
+        const std::string p = "l" + std::to_string(il) + ".", px = p + "mix.", pm = p + "mlp.";
+        const Json * ty = jl.get("type"), * mx = jl.get("mixer"), * ml = jl.get("mlp");
+        if (!ty || ty->kind != Json::STR || !mx) { pib_set_error("model: layer %d needs type and mixer", il); return nullptr; }
+        VEC(L.norm1, p + "norm1", W);
+        if (hy->taps > 0) { GET(p + "canon1", W, hy->taps); if (!(L.canon = upload_f32v(v))) return nullptr; L.tail_off = state; state += (size_t) (hy->taps - 1) * W; }
+        L.heads = (int) jnum(mx, "heads", 0); L.dim = (int) jnum(mx, "dim", 0); L.vdim = (int) jnum(mx, "vdim", 0);
+        if (L.heads <= 0 || L.dim <= 0 || L.vdim <= 0) { pib_set_error("model: layer %d: heads / dim / vdim", il); return nullptr; }
+        if (ty->str == "hgrn2") {
+            L.mixer = PIB_MIXER_HGRN2;
+            const int64_t HD = (int64_t) L.heads * L.dim, HV = (int64_t) L.heads * L.vdim;
+            std::vector<float> all;
+            GET(px + "q", HD, W); all = v;
+            GET(px + "f", HD, W); all.insert(all.end(), v.begin(), v.end());
+            GET(px + "v", HV, W); all.insert(all.end(), v.begin(), v.end());
+            if (!(L.qfv = upload_mat(all, 2 * HD + HV, W, dtype, m))) return nullptr;
+            VEC(L.f_bias, px + "f.b", HD);
+            VEC(L.lower, px + "lower", HD);
+            VEC(L.onorm, px + "norm", L.vdim);
+            MAT(L.wo, px + "o", W, HV);
+            L.state_off = state; state += (size_t) HD * L.vdim;
+            widen(hy->w_proj, 2 * HD + HV); widen(hy->w_att, HV);
+        } else if (ty->str == "latent_attention") {
+            L.mixer = PIB_MIXER_LATENT;
+            L.rot_dim = (int) jnum(mx, "rot_dim", 0); L.kv_rank = (int) jnum(mx, "kv_rank", 0); L.q_rank = (int) jnum(mx, "q_rank", 0);
+            L.scale = (float) jnum(mx, "scale", 1.0 / sqrt((double) (L.dim + L.rot_dim)));
+            const Json * mk = mx->get("mask"), * rt = mx->get("rot");
+            L.window = mk ? (int) jnum(mk, "size", 0) : 0;
+            if (L.window <= 0) L.window = 1 << 30;                              // no mask: every earlier token is seen
+            L.rot_base = (float) jnum(rt, "base", 10000.0); L.rot_dims = rt ? (int) jnum(rt, "dims", L.rot_dim) : 0;
+            L.kv_from = mx->get("kv_from") ? (int) jnum(mx, "kv_from", -1) : -1;
+            if (L.kv_rank <= 0 || L.q_rank <= 0 || L.rot_dim < 0 || L.rot_dims > L.rot_dim || (L.rot_dims & 1)) { pib_set_error("model: layer %d: kv_rank / q_rank / rot_dim / rot.dims", il); return nullptr; }
+            const int64_t H = L.heads, D = L.dim, rd = L.rot_dim, R = L.kv_rank, Q = L.q_rank;
+            std::vector<float> all;
+            GET(px + "dq", Q, W); all = v;
+            if (L.kv_from < 0) {
+                GET(px + "dkv", R + rd, W); all.insert(all.end(), v.begin(), v.end());
+                VEC(L.dkv_norm, px + "dkv.norm", R);
+                L.cache_id = hy->n_cache++;
+                hy->cache_row.push_back((int) (R + rd));
+            } else {
+                if (L.kv_from >= il || hy->layers[L.kv_from].mixer != PIB_MIXER_LATENT || hy->layers[L.kv_from].kv_from >= 0 ||
+                    hy->layers[L.kv_from].kv_rank != L.kv_rank || hy->layers[L.kv_from].rot_dim != L.rot_dim) {
+                    pib_set_error("model: layer %d: kv_from %d is not an earlier latent-attention layer with a cache of the same shape", il, L.kv_from);
+                    return nullptr;
+                }
+                L.cache_id = hy->layers[L.kv_from].cache_id;
+            }
+            if (!(L.dqkv = upload_mat(all, (int64_t) all.size() / W, W, dtype, m))) return nullptr;
+            VEC(L.dq_norm, px + "dq.norm", Q);
+            MAT(L.uq, px + "uq", H * (D + rd), Q);
+            GET(px + "uk", H * D, R);
+            {   // per head W_uk^T: [kv_rank][dim], so that folding a query through it is the same row-times-row product as every other matmul
+                std::vector<float> tr((size_t) (H * D * R));
+                for (int64_t h = 0; h < H; h++) for (int64_t d = 0; d < D; d++) for (int64_t r = 0; r < R; r++) tr[(size_t) ((h * R + r) * D + d)] = v[(size_t) ((h * D + d) * R + r)];
+                if (!(L.ukT = upload_mat(tr, H * R, D, dtype, m))) return nullptr;
+            }
+            MAT(L.uv, px + "uv", H * L.vdim, R);
+            VEC(L.sink, px + "sink", H);
+            MAT(L.wo, px + "o", W, H * L.vdim);
+            L.rope_id = -1;
+            for (size_t i = 0; i < hy->ropes.size(); i++) if (hy->ropes[i].base == L.rot_base && hy->ropes[i].dims == L.rot_dims) L.rope_id = (int) i;
+            if (L.rope_id < 0) { L.rope_id = (int) hy->ropes.size(); hy->ropes.push_back({ L.rot_base, L.rot_dims }); }
+            widen(hy->w_proj, Q + R + rd); widen(hy->w_cq, Q); widen(hy->w_q, H * (D + rd)); widen(hy->w_lat, H * R); widen(hy->w_att, H * L.vdim);
+        } else { pib_set_error("model: layer %d: unknown mixer '%s'", il, ty->str.c_str()); return nullptr; }
+        if (ml && !ml->is_null()) {
+            VEC(L.norm2, p + "norm2", W);
+            const Json * kind = ml->get("kind");
+            if (kind && kind->str == "dense") {
+                L.mlp = PIB_MLP_POLYNORM; L.ff = (int) jnum(ml, "ff", 0);
+                if (L.ff <= 0) { pib_set_error("model: layer %d: mlp.ff", il); return nullptr; }
+                MAT(L.up, pm + "up", L.ff, W);
+                MAT(L.down, pm + "down", W, L.ff);
+                GET(pm + "act", 4);
+                memcpy(L.act, v.data(), 16);
+                widen(hy->w_proj, L.ff);
+            } else if (kind && kind->str == "moe") {
+                L.mlp = PIB_MLP_MOE;
+                L.n_experts = (int) jnum(ml->get("router"), "experts", 0); L.top = (int) jnum(ml->get("router"), "top", 0);
+                L.ff_e = (int) jnum(ml->get("expert"), "ff", 0);
+                const Json * sh = ml->get("shared");
+                L.ff_s = sh && !sh->is_null() ? (int) jnum(sh, "ff", 0) : 0;
+                if (L.n_experts <= 0 || L.top <= 0 || L.top > L.n_experts || L.ff_e <= 0) { pib_set_error("model: layer %d: router.experts / router.top / expert.ff", il); return nullptr; }
+                std::vector<float> ups, downs;
+                for (int e = 0; e < L.n_experts; e++) {
+                    const std::string pe = pm + "e" + std::to_string(e) + ".";
+                    GET(pe + "up", L.ff_e, W); ups.insert(ups.end(), v.begin(), v.end());
+                    GET(pe + "down", W, L.ff_e); downs.insert(downs.end(), v.begin(), v.end());
+                }
+                if (!(L.e_up = upload_mat(ups, (int64_t) L.n_experts * L.ff_e, W, dtype, m)) || !(L.e_down = upload_mat(downs, (int64_t) L.n_experts * W, L.ff_e, dtype, m))) return nullptr;
+                GET(pm + "router", L.n_experts, W);
+                if (!(L.router = upload_mat(v, L.n_experts, W, PIB_TYPE_F32, m))) return nullptr;          // the router is always 32-bit
+                if (L.ff_s > 0) { MAT(L.s_up, pm + "shared.up", L.ff_s, W); MAT(L.s_down, pm + "shared.down", W, L.ff_s); widen(hy->w_proj, L.ff_s); }
+                widen(hy->w_pairs, L.top); widen(hy->w_eup, (int64_t) L.top * L.ff_e); widen(hy->w_router, L.n_experts);
+            } else { pib_set_error("model: layer %d: unknown mlp kind", il); return nullptr; }
+        }
+    }
+    hy->state_floats = state ? state : 4;
+#undef GET
+#undef VEC
+#undef MAT
+    return mp.release();
+}
+
+// ---- registry: config.json "architecture" -> builder ---------------------------------------------------------------------------------
+struct DirArch { const char * name; pib_model * (*build)(const Json &, TensorSource &, int); };
+static const DirArch DIR_ARCHS[] = { { "Rapisun", build_rapisun } };
+
+static pib_model * build_from_config(const Json & cfg, TensorSource & src, int dtype) {
+    const Json * a = cfg.get("architecture");
+    if (cfg.kind != Json::OBJ || !a || a->kind != Json::STR) { pib_set_error("model: config.json has no \"architecture\""); return nullptr; }
+    for (const DirArch & d : DIR_ARCHS) if (a->str == d.name) return d.build(cfg, src, dtype);
+    pib_set_error("model: unknown architecture '%s'", a->str.c_str());
+    return nullptr;
+}
+
+pib_model * pib_model_load_dir(const char * dir, int dtype) {
+    std::string d(dir), txt;
+    if (d.size() > 12 && !d.compare(d.size() - 12, 12, "/config.json")) d.resize(d.size() - 12);
+    if (!read_file(d + "/config.json", txt)) { pib_set_error("model: cannot read %s/config.json", d.c_str()); return nullptr; }
+    Json cfg;
+    if (!json_parse(txt.data(), txt.size(), cfg)) { pib_set_error("model: %s/config.json is not JSON", d.c_str()); return nullptr; }
+    SafeTensors st;
+    if (!st.open(d + "/model.safetensors")) return nullptr;
+    TensorSource src;
+    src.st = &st;
+    return build_from_config(cfg, src, dtype);
+}
+
+pib_model * pib_hybrid_synthetic(const char * config_json, uint64_t seed, int dtype) {
+    Json cfg;
+    if (!json_parse(config_json, strlen(config_json), cfg)) { pib_set_error("model: the configuration is not JSON"); return nullptr; }
+    TensorSource src;
+    src.seed = seed;
+    return build_from_config(cfg, src, dtype);
+}
+
+void pib_hybrid_model_free(pib_model * m) {
+    pib_hybrid * hy = m->hy;
+    if (!hy) return;
+    for (pib_hlayer & L : hy->layers) {
+        for (float * f : { L.norm1, L.norm2, L.canon, L.dq_norm, L.dkv_norm, L.sink, L.f_bias, L.lower, L.onorm }) if (f) cudaFree(f);
+        for (pib_weight * w : { L.dqkv, L.uq, L.ukT, L.uv, L.wo, L.qfv, L.up, L.down, L.e_up, L.e_down, L.router, L.s_up, L.s_down }) if (w) pib_weight_free(w);
+    }
+    if (hy->embd_norm) cudaFree(hy->embd_norm);
+    delete hy;
+    m->hy = nullptr;
+}

@@ -55,6 +55,12 @@ def api():
     L.llama_load_model_from_file.argtypes = [C.c_char_p, ModelParams]
     L.llama_pib_synthetic_model.restype = C.c_void_p
     L.llama_pib_synthetic_model.argtypes = [C.c_int] * 7 + [C.c_uint64, C.c_int, C.c_float]
+    L.llama_pib_load_model_dir.restype = C.c_void_p
+    L.llama_pib_load_model_dir.argtypes = [C.c_char_p, C.c_int]
+    L.llama_pib_synthetic_config_model.restype = C.c_void_p
+    L.llama_pib_synthetic_config_model.argtypes = [C.c_char_p, C.c_uint64, C.c_int]
+    L.llama_pib_set_state_slots.argtypes = [C.c_void_p, C.c_int]
+    L.llama_pib_state_slots_free.argtypes = [C.c_void_p]
     L.llama_free_model.argtypes = [C.c_void_p]
     L.llama_new_context_with_model.restype = C.c_void_p
     L.llama_new_context_with_model.argtypes = [C.c_void_p, ContextParams]
@@ -124,17 +130,27 @@ def make_batch(tokens, pos, seq_lists, batch_id=0, max_n_seq=1):
 class Context:
     """thin object wrapper: a model + a context through the llama.h-compatible ABI"""
 
-    def __init__(self, model_path=None, n_ctx=512, max_seq=64, synthetic=None):
+    def __init__(self, model_path=None, n_ctx=512, max_seq=64, synthetic=None, model_dir=None, config=None, float32=False, seed=0,
+                 state_slots=None):
+        """model_path: a GGUF file; synthetic: the tuple of llama_pib_synthetic_model; model_dir: a folder with config.json +
+        model.safetensors (layer-list designs); config: config.json text of such a design, weights drawn from `seed`.
+        float32 (folder / config models): everything in true 32-bit instead of bfloat16 operands."""
         self.L = api()
         self.L.llama_backend_init(False)
         if synthetic is not None:
             self.model = self.L.llama_pib_synthetic_model(*synthetic)
+        elif model_dir is not None:
+            self.model = self.L.llama_pib_load_model_dir(model_dir.encode(), 1 if float32 else 0)
+        elif config is not None:
+            self.model = self.L.llama_pib_synthetic_config_model(config.encode(), seed, 1 if float32 else 0)
         else:
             self.model = self.L.llama_load_model_from_file(model_path.encode(), self.L.llama_model_default_params())
         if not self.model:
             raise PibError(self.L.pib_last_error().decode())
         self.ctx = self.L.llama_pib_new_context(self.model, n_ctx, max_seq)
         if not self.ctx:
+            raise PibError(self.L.pib_last_error().decode())
+        if state_slots is not None and self.L.llama_pib_set_state_slots(self.ctx, state_slots) != 0:
             raise PibError(self.L.pib_last_error().decode())
         self.n_vocab = self.L.llama_n_vocab(self.model)
         self.n_ctx = n_ctx
@@ -156,6 +172,17 @@ class Context:
             p = self.L.llama_get_logits_ith(self.ctx, i)
             out[i] = np.ctypeslib.as_array(p, shape=(self.n_vocab,))
         return rc, out
+
+    def decode_rows(self, tokens, pos, seq_lists, rows):
+        """like decode(), but fetches only the logits rows named in `rows`"""
+        b, keep = make_batch(tokens, pos, seq_lists, self._bid, self.max_seq)
+        self._bid += 1
+        if self.L.llama_decode(self.ctx, b) != 0:
+            raise PibError(self.L.pib_last_error().decode())
+        out = np.empty((len(rows), self.n_vocab), dtype=np.float32)
+        for k, i in enumerate(rows):
+            out[k] = np.ctypeslib.as_array(self.L.llama_get_logits_ith(self.ctx, i), shape=(self.n_vocab,))
+        return out
 
     def start(self, tokens, pos, seq_lists, batch_id=None):
         if batch_id is None:
