@@ -230,3 +230,32 @@ pib_weight * pib_dense_upload(int type, const void * host, int64_t N, int64_t K)
     }
     return w;
 }
+
+// host-buffer convenience for the parity tests: every operand in host memory, shapes and strides as in pib_mm (elements).
+// W: bfloat16 bits (wtype PIB_TYPE_BF16) or float32; zrange / xrows may be null.
+extern "C" int pib_dense_mm_host(int wtype, const void * W, int64_t w_elems, int64_t ldw, int64_t wz, const float * X, int64_t x_elems, int64_t ldx, int64_t xz,
+                                 const int32_t * xrows, int xdiv, float * Y, int64_t y_elems, int64_t ldy, int64_t yz, int M, int N, int K, int Z,
+                                 const int32_t * zrange, int epi, int exact) {
+    const size_t wb = (size_t) w_elems * (wtype == PIB_TYPE_BF16 ? 2 : 4);
+    void * dW = nullptr; float * dX = nullptr, * dY = nullptr; int32_t * dR = nullptr, * dZ = nullptr;
+    int rc = PIB_OK;
+    if (cudaMalloc(&dW, wb + 256) != cudaSuccess || cudaMalloc(&dX, (size_t) x_elems * 4 + 256) != cudaSuccess || cudaMalloc(&dY, (size_t) y_elems * 4 + 256) != cudaSuccess ||
+        cudaMalloc(&dR, (size_t) M * 4 + 256) != cudaSuccess || cudaMalloc(&dZ, (size_t) (Z + 1) * 4 + 256) != cudaSuccess) rc = PIB_ERR_NOMEM;
+    if (rc == PIB_OK) {
+        cudaMemcpy(dW, W, wb, cudaMemcpyHostToDevice);
+        cudaMemcpy(dX, X, (size_t) x_elems * 4, cudaMemcpyHostToDevice);
+        cudaMemcpy(dY, Y, (size_t) y_elems * 4, cudaMemcpyHostToDevice);
+        if (xrows) cudaMemcpy(dR, xrows, (size_t) M * 4, cudaMemcpyHostToDevice);
+        if (zrange) cudaMemcpy(dZ, zrange, (size_t) (Z + 1) * 4, cudaMemcpyHostToDevice);
+        pib_mm a;
+        a.W = dW; a.wtype = wtype; a.ldw = ldw; a.wz = wz; a.X = dX; a.ldx = ldx; a.xz = xz; a.xrows = xrows ? dR : nullptr; a.xdiv = xdiv;
+        a.Y = dY; a.ldy = ldy; a.yz = yz; a.M = M; a.N = N; a.K = K; a.Z = Z; a.zrange = zrange ? dZ : nullptr; a.epi = epi; a.exact = exact;
+        rc = pib_dense_mm(a, nullptr);
+        if (rc == PIB_OK && wtype == PIB_TYPE_BF16 && !exact) { pib_dense_mm_check(nullptr, 1); }
+        if (rc == PIB_OK && cudaDeviceSynchronize() != cudaSuccess) { pib_set_error("dense matmul: %s", cudaGetErrorString(cudaGetLastError())); rc = PIB_ERR_CUDA; }
+        if (rc == PIB_OK && wtype == PIB_TYPE_BF16 && !exact) rc = pib_dense_mm_check(nullptr, 0);
+        if (rc == PIB_OK) cudaMemcpy(Y, dY, (size_t) y_elems * 4, cudaMemcpyDeviceToHost);
+    } else pib_set_error("dense matmul: out of memory for the test buffers");
+    for (void * p : { dW, (void *) dX, (void *) dY, (void *) dR, (void *) dZ }) if (p) cudaFree(p);
+    return rc;
+}

@@ -1167,6 +1167,7 @@ int pib_run_finish(pib_context * c, int run) {
     clear_cancel_flag(c, r.id);
     if (c->stage.size > 1 && c->stage.first()) pib_pipe_ship_ints(2, 0, &r.batch_id, 1);
     for (auto it = c->inflight.begin(); it != c->inflight.end(); ++it) if (*it == run) { c->inflight.erase(it); break; }
+    if (c->hy && c->model->wtype == PIB_TYPE_BF16 && pib_dense_mm_check(c->stream, 0) != PIB_OK) r.failed = true;   // a tensor-core kernel gave up on a wait
     r.in_use         = false;
     c->last_finished = run;     // its buffers stay reserved until the next finish (llama_get_logits_ith contract)
     c->logits_row_valid.assign((size_t) r.n_tokens, 0);

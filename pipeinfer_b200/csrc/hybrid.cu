@@ -319,6 +319,7 @@ int pib_hybrid_decode_start(pib_context * c, int n_tokens, const int32_t * token
         c->d2h_bytes += sizeof(pib_row_result) * (size_t) T;
         run->rows_on_host = true;
     }
+    if (hy->dtype == PIB_TYPE_BF16) pib_dense_mm_check(st, 1);
     cudaEventRecord(run->done, st);
     c->inflight.push_back(run->id);
     c->n_decode++;

@@ -86,6 +86,7 @@ struct pib_mm {
     int             exact = 0;                           // 1: operands stay fp32 (no bfloat16 rounding of X); W must be float32
 };
 int pib_dense_mm(const pib_mm & a, cudaStream_t st);
+int pib_dense_mm_check(cudaStream_t st, int enqueue);   // dense_mma.cu: the error word of the bounded waits (1: copy it in stream order, 0: read the copy)
 pib_weight * pib_dense_upload(int type, const void * host, int64_t N, int64_t K);   // type: PIB_TYPE_BF16 / PIB_TYPE_F32, row-major [N][K]
 
 // hybrid_kernels.cu

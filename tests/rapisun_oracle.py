@@ -250,6 +250,7 @@ def write_model(folder, cfg, W):
         json.dump(cfg, f)
     head, blobs, off = {}, [], 0
     for name, w in W.items():
+        assert np.array_equal(bf16_round(w), np.asarray(w, np.float64)), "%s is not bfloat16-representable: round it first" % name
         b = (np.asarray(w, np.float32).view(np.uint32) >> 16).astype(np.uint16).tobytes()
         head[name] = {"dtype": "BF16", "shape": list(np.shape(w)), "data_offsets": [off, off + len(b)]}
         blobs.append(b)
