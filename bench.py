@@ -231,10 +231,17 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-plain", action="store_true", help="skip the non-speculative generation after the timed steps (plain_tok_s, plain_tokens_sha)")
     ap.add_argument("--layer-split", default="", help="comma-separated per-stage weights, as the reference's --mpi-layer-split")
+    ap.add_argument("--design", default="", choices=["", "rapisun"],
+                    help="instead of the default workload: prefill / decode throughput and per-launch rooflines of a layer-list design beside the closest llama-arch model")
+    ap.add_argument("--design-size", default="w2048", help="comma-separated sizes of pipeinfer_b200/design_bench.py: w1024, w2048, w4096")
+    ap.add_argument("--design-prompt", default="512,2048", help="prompt lengths of the prefill measurement")
     ap.add_argument("--head-share", type=float, default=None, help="share of the target's layers on the head GPU (which also runs the draft)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.design:
+        from pipeinfer_b200 import design_bench
+        return design_bench.run(args) if rank == 0 else 0
     if args.max_spec_runs < 0:
         args.max_spec_runs = world + 1
     (L, E, H, HKV, FF, V, wt), dshape, label = CONFIGS[args.config]

@@ -17,7 +17,7 @@
 #define MM_BM 64
 #define MM_BN 64
 #define MM_BK 16
-#define MV_MAXB 8
+#define MV_MAXB 16
 
 __device__ __forceinline__ float round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 __device__ __forceinline__ float ld_w(const float * p) { return *p; }
@@ -145,6 +145,7 @@ __global__ void __launch_bounds__(256) mv_rows_kernel(mm_dev a) {
 #pragma unroll
     for (int b = 0; b < B; b++) acc[b] = 0.f;
     const int Kv = a.K - a.K % V;
+#pragma unroll 2
     for (int k = lane * V; k < Kv; k += 32 * V) {
         float w[V];
         wvec<WT>::load(W + k, w);
@@ -178,14 +179,14 @@ static int launch_mm(const pib_mm & a, const mm_dev & d, cudaStream_t st) {
     const int  V = wvec<WT>::N;
     // the row kernel wants aligned 16-byte weight loads: row stride, z stride and base all multiples of the vector
     const bool vec_ok = a.ldw % V == 0 && a.wz % V == 0 && ((uintptr_t) a.W & 15) == 0;
-    if (!a.zrange && a.M <= MV_MAXB && vec_ok) {
+    // few rows in all (with zrange: no problem z can own more than the total): a warp per weight row; problems without rows leave at once
+    if (a.M <= MV_MAXB && vec_ok) {
         dim3 grid((unsigned) ((a.N + 7) / 8), 1, (unsigned) a.Z);
-        switch (a.M) {
-            case 1: mv_rows_kernel<WT, ROUND, EPI, 1><<<grid, 256, 0, st>>>(d); break;
-            case 2: mv_rows_kernel<WT, ROUND, EPI, 2><<<grid, 256, 0, st>>>(d); break;
-            case 3: case 4: mv_rows_kernel<WT, ROUND, EPI, 4><<<grid, 256, 0, st>>>(d); break;
-            default: mv_rows_kernel<WT, ROUND, EPI, MV_MAXB><<<grid, 256, 0, st>>>(d); break;
-        }
+        if (a.M == 1)      mv_rows_kernel<WT, ROUND, EPI, 1><<<grid, 256, 0, st>>>(d);
+        else if (a.M == 2) mv_rows_kernel<WT, ROUND, EPI, 2><<<grid, 256, 0, st>>>(d);
+        else if (a.M <= 4) mv_rows_kernel<WT, ROUND, EPI, 4><<<grid, 256, 0, st>>>(d);
+        else if (a.M <= 8) mv_rows_kernel<WT, ROUND, EPI, 8><<<grid, 256, 0, st>>>(d);
+        else               mv_rows_kernel<WT, ROUND, EPI, MV_MAXB><<<grid, 256, 0, st>>>(d);
     } else {
         dim3 grid((unsigned) ((a.M + MM_BM - 1) / MM_BM), (unsigned) ((a.N + MM_BN - 1) / MM_BN), (unsigned) a.Z);
         mm_tile_kernel<WT, ROUND, EPI><<<grid, 256, 0, st>>>(d);

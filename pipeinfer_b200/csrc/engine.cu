@@ -498,7 +498,7 @@ static pib_context * hybrid_context_new(pib_model * m, uint32_t n_ctx, int max_s
     c->desc_slots  = 1;                                   // one zeroed descriptor: the sampler's launch contract
     CK(cudaMalloc(&c->desc_dev, c->desc_stride * 2));
     CK(cudaMemset(c->desc_dev, 0, c->desc_stride * 2));
-    c->use_graphs = false;
+    { const char * g = getenv("PIB_GRAPHS"); c->use_graphs = !g || atoi(g) != 0; }
     c->ops_cap = 1 << 12;
     CK(cudaMallocHost(&c->ops_host, sizeof(KvOp) * c->ops_cap));
     CK(cudaMalloc(&c->ops_dev, sizeof(KvOp) * c->ops_cap));

@@ -35,7 +35,33 @@ struct pib_hybrid_ctx {
     int32_t *   meta_dev = nullptr;
     int         meta_cap = 0, meta_next = 0;
     std::string kv_error;                       // set when a cache op arrived that the states cannot follow
+    // per-launch timing (llama_pib_profile_layer(ctx, >= 0) switches it on): CUDA events around every launch of every layer
+    struct Rec { int kind; double flops, bytes; cudaEvent_t e0, e1; };
+    std::vector<Rec> prof;
 };
+
+// kinds of launches, for the profile
+static const char * const HK_NAMES[] = { "cellmap", "embed_ln", "canon_conv", "mm_dq_dkv", "latent_prep", "mm_uq", "mm_absorb_uk", "latent_attention", "mm_uv", "mm_attn_o",
+                                         "mm_qfv", "hgrn2_gates", "hgrn2_scan", "mm_hgrn2_o", "ln_residual", "mm_up", "polynorm", "mm_down", "mm_router", "moe_route",
+                                         "moe_sort", "mm_experts_up", "mm_experts_down", "mm_shared_up", "mm_shared_down", "moe_combine", "final_ln", "mm_head", "sample" };
+enum { HK_CELLMAP, HK_EMBED, HK_CANON, HK_DQKV, HK_LPREP, HK_UQ, HK_ABSORB, HK_LATTN, HK_UV, HK_AO, HK_QFV, HK_GATES, HK_SCAN, HK_HO, HK_LNRES, HK_UP, HK_POLY, HK_DOWN,
+       HK_ROUTER, HK_ROUTE, HK_SORT, HK_EUP, HK_EDOWN, HK_SUP, HK_SDOWN, HK_COMBINE, HK_FINAL, HK_HEAD, HK_SAMPLE, HK_COUNT };
+const char * pib_hybrid_kind_name(int k) { return k >= 0 && k < HK_COUNT ? HK_NAMES[k] : "?"; }
+
+// fetch and clear the records; returns the count (the stream is synchronised)
+int pib_hybrid_profile_read(pib_context * c, int32_t * kind, float * ms, double * flops, double * bytes, int cap) {
+    if (!c->hy) return 0;
+    cudaStreamSynchronize(c->stream);
+    int n = 0;
+    for (auto & r : c->hy->prof) {
+        float t = 0.f;
+        cudaEventElapsedTime(&t, r.e0, r.e1);
+        if (n < cap) { kind[n] = r.kind; ms[n] = t; flops[n] = r.flops; bytes[n] = r.bytes; n++; }
+        cudaEventDestroy(r.e0); cudaEventDestroy(r.e1);
+    }
+    c->hy->prof.clear();
+    return n;
+}
 
 #define HCK(expr) do { if ((expr) != cudaSuccess) { pib_set_error("%s:%d %s: %s", __FILE__, __LINE__, #expr, cudaGetErrorString(cudaGetLastError())); return PIB_ERR_CUDA; } } while (0)
 
@@ -115,6 +141,8 @@ static int grow_scratch(pib_context * c, int T) {
     if (T <= x->cap) return PIB_OK;
     const pib_hybrid * hy = c->model->hy;
     cudaStreamSynchronize(c->stream);
+    for (auto & g : c->graphs) if (g.second.exec) cudaGraphExecDestroy(g.second.exec);        // they hold the old buffers' addresses
+    c->graphs.clear();
     free_scratch(x);
     const size_t n = (size_t) ((T + 63) / 64 * 64), W = (size_t) c->model->n_embd;
     auto fl = [&](float ** p, size_t per) { return per == 0 || cudaMalloc(p, n * per * 4) == cudaSuccess; };
@@ -130,7 +158,7 @@ static int grow_scratch(pib_context * c, int T) {
 }
 
 // ---- the layers -----------------------------------------------------------------------------------------------------------------------
-static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B) {
+static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B, const int32_t * B_pos_host) {
     pib_hybrid_ctx *   x  = c->hy;
     const pib_model *  m  = c->model;
     const pib_hybrid * hy = m->hy;
@@ -139,73 +167,89 @@ static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B) {
     const float eps = hy->eps;
     int rc;
     uint64_t & nk = c->n_kernels;
-#define RC(e) do { rc = (e); if (rc != PIB_OK) return rc; nk++; } while (0)
+    const bool profiling = c->prof_layer >= 0 && x->prof.size() < (1u << 16);
+    // one launch (or the few launches of one step) of kind k; fl / by: its floating-point operations and algorithmic bytes
+#define RC(k, fl, by, e) do {                                                                                        \
+        pib_hybrid_ctx::Rec r__ = { (k), (double) (fl), (double) (by), nullptr, nullptr };                           \
+        if (profiling) { cudaEventCreate(&r__.e0); cudaEventCreate(&r__.e1); cudaEventRecord(r__.e0, st); }          \
+        rc = (e);                                                                                                    \
+        if (profiling) { cudaEventRecord(r__.e1, st); x->prof.push_back(r__); }                                      \
+        if (rc != PIB_OK) return rc;                                                                                 \
+        nk++;                                                                                                        \
+    } while (0)
+    const double Td = T, Wd = W;
+    auto wbytes = [](const pib_weight * w) { return (double) w->bytes; };
+    auto mmfl = [&](const pib_weight * w) { return 2.0 * Td * (double) w->N * (double) w->K; };
+    auto mmby = [&](const pib_weight * w) { return (double) w->bytes + 4.0 * Td * ((double) w->N + (double) w->K); };
+    auto key_pairs = [&](int window) { double n = 0; for (int i = 0; i < T; i++) n += std::min(B_pos_host[i] + 1, window); return n; };
     auto mm = [&](const pib_weight * w, const float * X, int ldx, float * Y, int ldy, int epi) {
         pib_mm a;
         a.W = w->base; a.wtype = w->type; a.ldw = w->K; a.X = X; a.ldx = ldx; a.Y = Y; a.ldy = ldy; a.M = T; a.N = (int) w->N; a.K = (int) w->K; a.epi = epi;
         a.exact = exact || w->type == PIB_TYPE_F32;
         return pib_dense_mm(a, st);
     };
-    RC(pib_cellmap_set(x->cellmap, (int) c->n_ctx, B, st));
-    RC(pib_embed_ln(m->tok_embd, B.tok, hy->embd_norm, eps, T, W, x->x, st));
+    RC(HK_CELLMAP, 0, 16.0 * Td, pib_cellmap_set(x->cellmap, (int) c->n_ctx, B, st));
+    RC(HK_EMBED, 0, 6.0 * Td * Wd, pib_embed_ln(m->tok_embd, B.tok, hy->embd_norm, eps, T, W, x->x, st));
     for (int il = 0; il < m->n_layer; il++) {
         const pib_hlayer & L = hy->layers[il];
         const float * hin = x->x;
-        if (L.canon) { RC(pib_canon_conv(x->x, L.canon, hy->taps, B, x->state, hy->state_floats, L.tail_off, W, x->h, st)); nk += hy->taps > 1; hin = x->h; }
+        if (L.canon) { RC(HK_CANON, 2.0 * Td * Wd * hy->taps, 8.0 * Td * Wd, pib_canon_conv(x->x, L.canon, hy->taps, B, x->state, hy->state_floats, L.tail_off, W, x->h, st)); nk += hy->taps > 1; hin = x->h; }
         if (L.mixer == PIB_MIXER_LATENT) {
             const int H = L.heads, D = L.dim, rd = L.rot_dim, R = L.kv_rank, V = L.vdim, ldp = (int) L.dqkv->N, row = hy->cache_row[L.cache_id];
             float * cache = x->cache[L.cache_id];
-            RC(mm(L.dqkv, hin, W, x->proj, ldp, PIB_EPI_NONE));
-            RC(pib_latent_prep(x->proj, ldp, L, L.dq_norm, L.dkv_norm, eps, B, x->rope[L.rope_id], (int) c->n_ctx, x->cq, L.kv_from < 0 ? cache : nullptr, row, st));
-            RC(mm(L.uq, x->cq, L.q_rank, x->q, H * (D + rd), PIB_EPI_NONE));
+            const double keys = key_pairs(L.window);
+            RC(HK_DQKV, mmfl(L.dqkv), mmby(L.dqkv), mm(L.dqkv, hin, W, x->proj, ldp, PIB_EPI_NONE));
+            RC(HK_LPREP, 0, 8.0 * Td * ldp, pib_latent_prep(x->proj, ldp, L, L.dq_norm, L.dkv_norm, eps, B, x->rope[L.rope_id], (int) c->n_ctx, x->cq, L.kv_from < 0 ? cache : nullptr, row, st));
+            RC(HK_UQ, mmfl(L.uq), mmby(L.uq), mm(L.uq, x->cq, L.q_rank, x->q, H * (D + rd), PIB_EPI_NONE));
             {   // q_lat[t][h] = W_uk,h^T q_unrotated[t][h]: one problem per head
                 pib_mm a;
                 a.W = L.ukT->base; a.wtype = L.ukT->type; a.ldw = D; a.wz = (int64_t) R * D; a.X = x->q; a.ldx = (int64_t) H * (D + rd); a.xz = D + rd;
                 a.Y = x->qlat; a.ldy = (int64_t) H * R; a.yz = R; a.M = T; a.N = R; a.K = D; a.Z = H; a.exact = exact;
-                RC(pib_dense_mm(a, st));
+                RC(HK_ABSORB, 2.0 * Td * H * R * D, wbytes(L.ukT) + 4.0 * Td * H * (D + R), pib_dense_mm(a, st));
             }
-            RC(pib_latent_attention(x->q, x->qlat, L, B, x->rope[L.rope_id], (int) c->n_ctx, cache, row, x->cellmap, (int) c->n_ctx, x->lat, st));
+            RC(HK_LATTN, 4.0 * keys * H * (R + rd), 4.0 * keys * (R + rd) + 8.0 * Td * H * R, pib_latent_attention(x->q, x->qlat, L, B, x->rope[L.rope_id], (int) c->n_ctx, cache, row, x->cellmap, (int) c->n_ctx, x->lat, st));
             {   // value of head h = W_uv,h (sum_j p_j c_j)
                 pib_mm a;
                 a.W = L.uv->base; a.wtype = L.uv->type; a.ldw = R; a.wz = (int64_t) V * R; a.X = x->lat; a.ldx = (int64_t) H * R; a.xz = R;
                 a.Y = x->att; a.ldy = (int64_t) H * V; a.yz = V; a.M = T; a.N = V; a.K = R; a.Z = H; a.exact = exact;
-                RC(pib_dense_mm(a, st));
+                RC(HK_UV, 2.0 * Td * H * R * V, wbytes(L.uv) + 4.0 * Td * H * (V + R), pib_dense_mm(a, st));
             }
-            RC(mm(L.wo, x->att, H * V, x->y, W, PIB_EPI_NONE));
+            RC(HK_AO, mmfl(L.wo), mmby(L.wo), mm(L.wo, x->att, H * V, x->y, W, PIB_EPI_NONE));
         } else {
             const int H = L.heads, HD = H * L.dim, ldp = (int) L.qfv->N;
-            RC(mm(L.qfv, hin, W, x->proj, ldp, PIB_EPI_NONE));
-            RC(pib_hgrn2_gates(x->proj, ldp, L.f_bias, L.lower, T, HD, st));
-            RC(pib_hgrn2_scan(x->proj, ldp, L, B, x->state, hy->state_floats, L.onorm, eps, x->att, st)); nk++;
-            RC(mm(L.wo, x->att, H * L.vdim, x->y, W, PIB_EPI_NONE));
+            RC(HK_QFV, mmfl(L.qfv), mmby(L.qfv), mm(L.qfv, hin, W, x->proj, ldp, PIB_EPI_NONE));
+            RC(HK_GATES, 0, 16.0 * Td * HD, pib_hgrn2_gates(x->proj, ldp, L.f_bias, L.lower, T, HD, st));
+            RC(HK_SCAN, 5.0 * Td * HD * L.vdim, 4.0 * Td * ldp + 8.0 * Td * H * L.vdim, pib_hgrn2_scan(x->proj, ldp, L, B, x->state, hy->state_floats, L.onorm, eps, x->att, st)); nk++;
+            RC(HK_HO, mmfl(L.wo), mmby(L.wo), mm(L.wo, x->att, H * L.vdim, x->y, W, PIB_EPI_NONE));
         }
-        RC(pib_layer_norm(x->y, L.norm1, eps, T, W, x->x, 1, st));
+        RC(HK_LNRES, 0, 12.0 * Td * Wd, pib_layer_norm(x->y, L.norm1, eps, T, W, x->x, 1, st));
         if (L.mlp == PIB_MLP_POLYNORM) {
-            RC(mm(L.up, x->x, W, x->proj, L.ff, PIB_EPI_NONE));
-            RC(pib_polynorm(x->proj, T, L.ff, L.act, eps, st));
-            RC(mm(L.down, x->proj, L.ff, x->y, W, PIB_EPI_NONE));
-            RC(pib_layer_norm(x->y, L.norm2, eps, T, W, x->x, 1, st));
+            RC(HK_UP, mmfl(L.up), mmby(L.up), mm(L.up, x->x, W, x->proj, L.ff, PIB_EPI_NONE));
+            RC(HK_POLY, 0, 8.0 * Td * L.ff, pib_polynorm(x->proj, T, L.ff, L.act, eps, st));
+            RC(HK_DOWN, mmfl(L.down), mmby(L.down), mm(L.down, x->proj, L.ff, x->y, W, PIB_EPI_NONE));
+            RC(HK_LNRES, 0, 12.0 * Td * Wd, pib_layer_norm(x->y, L.norm2, eps, T, W, x->x, 1, st));
         } else if (L.mlp == PIB_MLP_MOE) {
             const int E = L.n_experts, top = L.top, P = T * top;
-            RC(mm(L.router, x->x, W, x->rlog, E, PIB_EPI_NONE));
-            RC(pib_moe_route(x->rlog, T, E, top, x->ids, x->wts, st));
-            RC(pib_moe_sort(x->ids, P, E, x->counts, x->offs, x->perm, x->inv, st)); nk++;
+            const double touched = P >= E ? 1.0 : (double) P / E;          // weights of experts without a row are not read
+            RC(HK_ROUTER, mmfl(L.router), mmby(L.router), mm(L.router, x->x, W, x->rlog, E, PIB_EPI_NONE));
+            RC(HK_ROUTE, 0, 4.0 * Td * E, pib_moe_route(x->rlog, T, E, top, x->ids, x->wts, st));
+            RC(HK_SORT, 0, 4.0 * P * (E + 3.0), pib_moe_sort(x->ids, P, E, x->counts, x->offs, x->perm, x->inv, st)); nk++;
             {   // up-projection of every (token, expert) pair, pairs grouped by expert; relu^2 on the way out
                 pib_mm a;
                 a.W = L.e_up->base; a.wtype = L.e_up->type; a.ldw = W; a.wz = (int64_t) L.ff_e * W; a.X = x->x; a.ldx = W; a.xrows = x->perm; a.xdiv = top;
                 a.Y = x->eup; a.ldy = L.ff_e; a.M = P; a.N = L.ff_e; a.K = W; a.Z = E; a.zrange = x->offs; a.epi = PIB_EPI_RELU2; a.exact = exact;
-                RC(pib_dense_mm(a, st));
+                RC(HK_EUP, 2.0 * P * L.ff_e * Wd, wbytes(L.e_up) * touched + 4.0 * P * (Wd + L.ff_e), pib_dense_mm(a, st));
                 pib_mm b;
                 b.W = L.e_down->base; b.wtype = L.e_down->type; b.ldw = L.ff_e; b.wz = (int64_t) W * L.ff_e; b.X = x->eup; b.ldx = L.ff_e;
                 b.Y = x->edn; b.ldy = W; b.M = P; b.N = W; b.K = L.ff_e; b.Z = E; b.zrange = x->offs; b.exact = exact;
-                RC(pib_dense_mm(b, st));
+                RC(HK_EDOWN, 2.0 * P * L.ff_e * Wd, wbytes(L.e_down) * touched + 4.0 * P * (Wd + L.ff_e), pib_dense_mm(b, st));
             }
             if (L.s_up) {
-                RC(mm(L.s_up, x->x, W, x->proj, L.ff_s, PIB_EPI_RELU2));
-                RC(mm(L.s_down, x->proj, L.ff_s, x->ysh, W, PIB_EPI_NONE));
+                RC(HK_SUP, mmfl(L.s_up), mmby(L.s_up), mm(L.s_up, x->x, W, x->proj, L.ff_s, PIB_EPI_RELU2));
+                RC(HK_SDOWN, mmfl(L.s_down), mmby(L.s_down), mm(L.s_down, x->proj, L.ff_s, x->ysh, W, PIB_EPI_NONE));
             }
-            RC(pib_moe_combine(L.s_up ? x->ysh : nullptr, x->edn, x->wts, x->inv, T, top, W, x->y, st));
-            RC(pib_layer_norm(x->y, L.norm2, eps, T, W, x->x, 1, st));
+            RC(HK_COMBINE, 2.0 * P * Wd, 4.0 * Wd * (P + 2.0 * Td), pib_moe_combine(L.s_up ? x->ysh : nullptr, x->edn, x->wts, x->inv, T, top, W, x->y, st));
+            RC(HK_LNRES, 0, 12.0 * Td * Wd, pib_layer_norm(x->y, L.norm2, eps, T, W, x->x, 1, st));
         }
         if (const char * dump = getenv("PIB_HYBRID_DUMP")) {          // debugging: the residual stream after every layer, one file per layer and decode
             std::vector<float> hb((size_t) T * W);
@@ -216,9 +260,9 @@ static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B) {
             if (FILE * f = fopen(path, "wb")) { fwrite(hb.data(), 4, hb.size(), f); fclose(f); }
         }
     }
-    RC(pib_layer_norm(x->x, m->output_norm, eps, T, W, x->h, 0, st));
-    RC(mm(m->output, x->h, W, run.logits, m->n_vocab, PIB_EPI_NONE));
-    RC(pib_sample_topk(run.logits, T, m->n_vocab, c->bias_ids_dev, c->bias_val_dev, c->n_bias, run.res_dev, c->desc_dev, c->cancel_table, st));
+    RC(HK_FINAL, 0, 8.0 * Td * Wd, pib_layer_norm(x->x, m->output_norm, eps, T, W, x->h, 0, st));
+    RC(HK_HEAD, mmfl(m->output), mmby(m->output), mm(m->output, x->h, W, run.logits, m->n_vocab, PIB_EPI_NONE));
+    RC(HK_SAMPLE, 0, 4.0 * Td * m->n_vocab, pib_sample_topk(run.logits, T, m->n_vocab, c->bias_ids_dev, c->bias_val_dev, c->n_bias, run.res_dev, c->desc_dev, c->cancel_table, st));
 #undef RC
     return PIB_OK;
 }
@@ -283,6 +327,8 @@ int pib_hybrid_decode_start(pib_context * c, int n_tokens, const int32_t * token
     const int S = (int) segs.size(), words = 5 * T + 3 * S;
     if (words > x->meta_cap) {
         cudaStreamSynchronize(st);
+        for (auto & g : c->graphs) if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
+        c->graphs.clear();
         for (int i = 0; i < pib_hybrid_ctx::RING; i++) { if (x->meta_host[i]) cudaFreeHost(x->meta_host[i]); x->meta_host[i] = nullptr; }
         if (x->meta_dev) cudaFree(x->meta_dev);
         x->meta_cap = words * 2 + 64;
@@ -313,7 +359,35 @@ int pib_hybrid_decode_start(pib_context * c, int n_tokens, const int32_t * token
     run->in_use = true; run->batch_id = batch_id; run->n_tokens = T; run->failed = false; run->has_walk = false;
     c->tree_pending.n_branches = 0;
     cudaMemcpyAsync(c->cancel_table, c->run_id_host + run->id, sizeof(int), cudaMemcpyHostToDevice, st);
-    if (run_layers(c, *run, B) != PIB_OK) run->failed = true;
+    // decode steps (few tokens) are launch-bound: like the other architectures' single-chunk decodes they replay a CUDA graph, captured on
+    // the second use of its shape.  Every address a kernel gets is fixed for a given (tokens, segments, run slot); what varies between
+    // steps (tokens, positions, cells, slots) lives in the bookkeeping block on the device.
+    bool done = false;
+    if (c->use_graphs && T <= 16 && c->prof_layer < 0 && !getenv("PIB_HYBRID_DUMP")) {
+        pib_context::GraphEntry & g = c->graphs[(T << 16) | (S << 8) | run->id];
+        g.uses++;
+        if (!g.exec && !g.failed && g.uses >= 2) {
+            const uint64_t k0 = c->n_kernels;
+            cudaGraph_t graph = nullptr;
+            bool ok = cudaStreamBeginCapture(st, cudaStreamCaptureModeRelaxed) == cudaSuccess;
+            if (ok) {
+                const int rc = run_layers(c, *run, B, pos);
+                ok = cudaStreamEndCapture(st, &graph) == cudaSuccess && rc == PIB_OK && graph != nullptr;
+            }
+            if (ok) ok = cudaGraphInstantiate(&g.exec, graph, 0) == cudaSuccess;
+            if (graph) cudaGraphDestroy(graph);
+            g.n_kernels = (int) (c->n_kernels - k0);
+            c->n_kernels = k0;
+            if (!ok) { cudaGetLastError(); g.exec = nullptr; g.failed = true; }
+        }
+        if (g.exec) {
+            if (cudaGraphLaunch(g.exec, st) != cudaSuccess) { pib_set_error("decode: graph launch failed: %s", cudaGetErrorString(cudaGetLastError())); run->failed = true; }
+            c->n_kernels += (uint64_t) g.n_kernels;
+            c->n_graph_launches++;
+            done = true;
+        }
+    }
+    if (!done && run_layers(c, *run, B, pos) != PIB_OK) run->failed = true;
     if (!run->failed) {
         cudaMemcpyAsync(run->res_host, run->res_dev, sizeof(pib_row_result) * (size_t) T, cudaMemcpyDeviceToHost, st);
         c->d2h_bytes += sizeof(pib_row_result) * (size_t) T;

@@ -69,6 +69,8 @@ int         pib_hybrid_ctx_init(pib_context * c, int n_slots);
 void        pib_hybrid_ctx_free(pib_context * c);
 int         pib_hybrid_set_slots(pib_context * c, int n_slots);
 int         pib_hybrid_slots_free(const pib_context * c);
+const char * pib_hybrid_kind_name(int kind);
+int         pib_hybrid_profile_read(pib_context * c, int32_t * kind, float * ms, double * flops, double * bytes, int cap);
 void        pib_hybrid_on_kv_ops(pib_context * c, const std::vector<KvOp> & ops);
 int         pib_hybrid_decode_start(pib_context * c, int n_tokens, const int32_t * token, const int32_t * pos, const int32_t * n_seq_id,
                                     const int32_t * const * seq_id, int batch_id);

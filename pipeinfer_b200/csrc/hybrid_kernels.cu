@@ -257,7 +257,8 @@ int pib_latent_attention(const float * q, const float * qlat, const pib_hlayer &
                          const float * cache, int cache_row, const int32_t * cellmap, int n_ctx, float * ctx, cudaStream_t st) {
     (void) rope_n_pos;
     const int H = L.heads, R = L.kv_rank;
-    const int HPB = H < 4 ? H : 4;
+    // few tokens (decoding): one head per CTA and 16 key shares, so that a step still fills some of the machine
+    const int HPB = (long long) b.T * H <= 1024 ? 1 : (H < 4 ? H : 4);
     int KS = 16 / HPB;
     if (L.window < 64) KS = 1;
     while (KS > 1 && (size_t) HPB * KS * (R + 2) * 4 > 160 * 1024) KS >>= 1;
@@ -295,39 +296,57 @@ int pib_hgrn2_gates(float * qfv, int ld, const float * f_bias, const float * low
     return PIB_OK;
 }
 
-// grid (segment, head), 4 * vdim threads: thread (vd, part) keeps rows d = part + 4 r of column vd of the head's matrix in registers,
-// walks the segment's tokens in order and leaves the matrix in the slot.  The four parts of a column sit in neighbouring lanes.
+// grid (segment, head, tile of 32 value columns), 128 threads: thread (vd, part) keeps rows d = part + 4 r of column vd of the head's matrix
+// in registers (columns are independent, so a head's matrix is spread over vdim / 32 CTAs), walks the segment's tokens in order and
+// leaves the matrix in the slot.  The tokens' q, f and v come through shared memory in chunks of HG_CHUNK tokens (coalesced loads, one
+// barrier pair per chunk) instead of one dependent global load per token.  The four parts of a column sit in neighbouring lanes.
+#define HG_CHUNK 16
+#define HG_VT    32
 template <int ROWS>
-__global__ void __launch_bounds__(512) hgrn2_scan_kernel(const float * __restrict__ qfv, int ld, int H, int D, int V, const int32_t * __restrict__ seg_start,
-                                                          const int32_t * __restrict__ seg_len, const int32_t * __restrict__ seg_slot, float * __restrict__ state,
-                                                          size_t state_stride, size_t state_off, float * __restrict__ out) {
-    const int sg = blockIdx.x, h = blockIdx.y, part = threadIdx.x & 3, vd = threadIdx.x >> 2;
-    const int s0 = seg_start[sg], n = seg_len[sg];
+__global__ void __launch_bounds__(128) hgrn2_scan_kernel(const float * __restrict__ qfv, int ld, int H, int D, int V, const int32_t * __restrict__ seg_start,
+                                                         const int32_t * __restrict__ seg_len, const int32_t * __restrict__ seg_slot, float * __restrict__ state,
+                                                         size_t state_stride, size_t state_off, float * __restrict__ out) {
+    extern __shared__ float hs[];                  // [HG_CHUNK][2 D + HG_VT]
+    const int sg = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * HG_VT, part = threadIdx.x & 3, vl = threadIdx.x >> 2, vd = v0 + vl;
+    const int s0 = seg_start[sg], n = seg_len[sg], HD = H * D, row_f = 2 * D + HG_VT;
+    const bool vok = vd < V;
     float *   S = state + (size_t) seg_slot[sg] * state_stride + state_off + (size_t) h * D * V;
     float s[ROWS];
 #pragma unroll
-    for (int r = 0; r < ROWS; r++) { const int d = part + 4 * r; s[r] = d < D ? S[(size_t) d * V + vd] : 0.f; }
-    const int HD = H * D;
-    for (int i = 0; i < n; i++) {
-        const float * row = qfv + (size_t) (s0 + i) * ld;
-        const float * qp = row + (size_t) h * D, * fp = row + HD + (size_t) h * D;
-        const float   v = row[2 * HD + (size_t) h * V + vd];
-        float acc = 0.f;
-#pragma unroll
-        for (int r = 0; r < ROWS; r++) {
-            const int d = part + 4 * r;
-            if (d < D) {
-                const float f = fp[d];
-                s[r] = fmaf(f, s[r], (1.0f - f) * v);
-                acc = fmaf(qp[d], s[r], acc);
-            }
+    for (int r = 0; r < ROWS; r++) { const int d = part + 4 * r; s[r] = (d < D && vok) ? S[(size_t) d * V + vd] : 0.f; }
+    for (int c0 = 0; c0 < n; c0 += HG_CHUNK) {
+        const int nc = min(HG_CHUNK, n - c0);
+        __syncthreads();
+        for (int i = threadIdx.x; i < nc * row_f; i += blockDim.x) {
+            const int t = i / row_f, e = i % row_f;
+            const float * row = qfv + (size_t) (s0 + c0 + t) * ld;
+            float v;
+            if (e < D)          v = row[(size_t) h * D + e];
+            else if (e < 2 * D) v = row[HD + (size_t) h * D + (e - D)];
+            else                v = v0 + (e - 2 * D) < V ? row[2 * HD + (size_t) h * V + v0 + (e - 2 * D)] : 0.f;
+            hs[i] = v;
         }
-        acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-        acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-        if (part == 0) out[(size_t) (s0 + i) * H * V + (size_t) h * V + vd] = acc;
+        __syncthreads();
+        for (int t = 0; t < nc; t++) {
+            const float * qp = hs + t * row_f, * fp = qp + D;
+            const float   v = qp[2 * D + vl];
+            float acc = 0.f;
+#pragma unroll
+            for (int r = 0; r < ROWS; r++) {
+                const int d = part + 4 * r;
+                if (d < D) {
+                    const float f = fp[d];
+                    s[r] = fmaf(f, s[r], (1.0f - f) * v);
+                    acc = fmaf(qp[d], s[r], acc);
+                }
+            }
+            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+            if (part == 0 && vok) out[(size_t) (s0 + c0 + t) * H * V + (size_t) h * V + vd] = acc;
+        }
     }
 #pragma unroll
-    for (int r = 0; r < ROWS; r++) { const int d = part + 4 * r; if (d < D) S[(size_t) d * V + vd] = s[r]; }
+    for (int r = 0; r < ROWS; r++) { const int d = part + 4 * r; if (d < D && vok) S[(size_t) d * V + vd] = s[r]; }
 }
 
 // one warp per (token, head): o <- o / sqrt(mean(o^2) + eps) * w
@@ -344,12 +363,13 @@ __global__ void head_rmsnorm_kernel(float * __restrict__ o, int n_rows, int V, c
 int pib_hgrn2_scan(const float * qfv, int ld, const pib_hlayer & L, const pib_hbatch & b, float * state, size_t state_stride, const float * onorm, float eps,
                    float * out, cudaStream_t st) {
     const int H = L.heads, D = L.dim, V = L.vdim;
-    if (V * 4 > 512 || (V * 4) % 32 != 0 || D > 256) { pib_set_error("hgrn2: dim %d / vdim %d not supported (vdim a multiple of 8 up to 128, dim up to 256)", D, V); return PIB_ERR_UNSUPP; }
-    dim3 grid((unsigned) b.S, (unsigned) H);
-    const int rows = (D + 3) / 4;
-    if (rows <= 16)      hgrn2_scan_kernel<16><<<grid, V * 4, 0, st>>>(qfv, ld, H, D, V, b.seg_start, b.seg_len, b.seg_slot, state, state_stride, L.state_off, out);
-    else if (rows <= 32) hgrn2_scan_kernel<32><<<grid, V * 4, 0, st>>>(qfv, ld, H, D, V, b.seg_start, b.seg_len, b.seg_slot, state, state_stride, L.state_off, out);
-    else                 hgrn2_scan_kernel<64><<<grid, V * 4, 0, st>>>(qfv, ld, H, D, V, b.seg_start, b.seg_len, b.seg_slot, state, state_stride, L.state_off, out);
+    if (D > 256) { pib_set_error("hgrn2: dim %d not supported (up to 256)", D); return PIB_ERR_UNSUPP; }
+    dim3 grid((unsigned) b.S, (unsigned) H, (unsigned) ((V + HG_VT - 1) / HG_VT));
+    const int    rows = (D + 3) / 4;
+    const size_t smem = (size_t) HG_CHUNK * (2 * D + HG_VT) * 4;
+    if (rows <= 16)      hgrn2_scan_kernel<16><<<grid, 128, smem, st>>>(qfv, ld, H, D, V, b.seg_start, b.seg_len, b.seg_slot, state, state_stride, L.state_off, out);
+    else if (rows <= 32) hgrn2_scan_kernel<32><<<grid, 128, smem, st>>>(qfv, ld, H, D, V, b.seg_start, b.seg_len, b.seg_slot, state, state_stride, L.state_off, out);
+    else                 hgrn2_scan_kernel<64><<<grid, 128, smem, st>>>(qfv, ld, H, D, V, b.seg_start, b.seg_len, b.seg_slot, state, state_stride, L.state_off, out);
     CKL();
     const int n_rows = b.T * H;
     head_rmsnorm_kernel<<<(n_rows + 7) / 8, 256, 0, st>>>(out, n_rows, V, onorm, eps);

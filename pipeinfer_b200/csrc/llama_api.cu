@@ -629,6 +629,12 @@ extern "C" int llama_pib_profile_read(struct llama_context * ctx, int32_t * kind
     c->prof.clear();
     return n;
 }
+// layer-list models: every launch of every layer is timed while llama_pib_profile_layer(ctx, >= 0) is on; records carry the kind of
+// launch (name: llama_pib_hybrid_kind_name), its milliseconds, floating-point operations and algorithmic bytes
+extern "C" int llama_pib_hybrid_profile_read(struct llama_context * ctx, int32_t * kind, float * ms, double * flops, double * bytes, int cap) {
+    return pib_hybrid_profile_read(ctx->c, kind, ms, flops, bytes, cap);
+}
+extern "C" const char * llama_pib_hybrid_kind_name(int kind) { return pib_hybrid_kind_name(kind); }
 // shape of a resident matrix: N, K, algorithmic bytes (kind as above; layer ignored for the lm_head)
 extern "C" int llama_pib_matrix_shape(const struct llama_model * model, int layer, int kind, int64_t * N, int64_t * K, uint64_t * bytes) {
     const pib_model * m = model->m;
