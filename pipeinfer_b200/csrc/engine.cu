@@ -935,6 +935,11 @@ pib_run * pib_take_run(pib_context * c, int n_tokens) {
         const int cap = ((n_tokens + PIB_CHUNK - 1) / PIB_CHUNK) * PIB_CHUNK;
         if ((c->stage.last() || c->stage.first()) && r.cap_tokens < cap) {
             if (r.res_dev) { cudaStreamSynchronize(c->stream); cudaFree(r.logits); cudaFree(r.res_dev); cudaFreeHost(r.res_host); }
+            if (c->hy) {        // a layer-list model's graphs include the output matmul and the sampler: they hold this run's old buffers
+                cudaStreamSynchronize(c->stream);
+                for (auto & g : c->graphs) if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
+                c->graphs.clear();
+            }
             r.logits = nullptr; r.res_dev = nullptr; r.res_host = nullptr;
             if ((c->stage.last() && cudaMalloc(&r.logits, (size_t) cap * c->model->n_vocab * 4) != cudaSuccess) ||
                 cudaMalloc(&r.res_dev, (size_t) cap * sizeof(pib_row_result)) != cudaSuccess ||

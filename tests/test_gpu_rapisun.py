@@ -248,6 +248,21 @@ def test_long_decoding(tmp_path):
     assert e.max() < TOL32 and e[-20:].max() < TOL32
 
 
+def test_decode_steps_around_growing_prompts(tmp_path):
+    """single-token steps are replayed from captured graphs; a later, longer prompt makes the context grow its buffers (logits rows of a
+    run slot, work buffers), and the steps after it must not run on the old ones"""
+    cfg = CONFIGS["mixed_small"]()
+    W = O.random_weights(cfg, 22)
+    s = Served(tmp_path, cfg, W, n_ctx=512)
+    for r, n_prompt in enumerate([5, 40, 18, 130, 70]):
+        toks = tokens(cfg, n_prompt + 9, 30 + r)
+        ref = oracle_logits(cfg, W, toks)
+        got = s.feed(r, toks, [n_prompt] + list(range(n_prompt + 1, n_prompt + 9)))
+        s.end(r)
+        assert row_err(got, ref).max() < TOL32, "request %d" % r
+    s.close()
+
+
 @pytest.mark.parametrize("float32", [True, False])
 def test_greedy_generation_through_the_scheduler(tmp_path, float32):
     from pipeinfer_b200 import llama
