@@ -34,6 +34,9 @@ struct pib_hybrid_ctx {
     cudaEvent_t meta_ev[RING]   = { nullptr, nullptr, nullptr, nullptr };
     int32_t *   meta_dev = nullptr;
     int         meta_cap = 0, meta_next = 0;
+    // operands of the matmul form of the attention: keys [NK][row] and transposed latents [R][NKp] (bfloat16), query rows, score rows
+    void * am_kb = nullptr, * am_vt = nullptr; float * am_q = nullptr, * am_s = nullptr;
+    size_t am_kb_cap = 0, am_vt_cap = 0, am_q_cap = 0, am_s_cap = 0;
     std::string kv_error;                       // set when a cache op arrived that the states cannot follow
     // per-launch timing (llama_pib_profile_layer(ctx, >= 0) switches it on): CUDA events around every launch of every layer
     struct Rec { int kind; double flops, bytes; cudaEvent_t e0, e1; };
@@ -43,9 +46,9 @@ struct pib_hybrid_ctx {
 // kinds of launches, for the profile
 static const char * const HK_NAMES[] = { "cellmap", "embed_ln", "canon_conv", "mm_dq_dkv", "latent_prep", "mm_uq", "mm_absorb_uk", "latent_attention", "mm_uv", "mm_attn_o",
                                          "mm_qfv", "hgrn2_gates", "hgrn2_scan", "mm_hgrn2_o", "ln_residual", "mm_up", "polynorm", "mm_down", "mm_router", "moe_route",
-                                         "moe_sort", "mm_experts_up", "mm_experts_down", "mm_shared_up", "mm_shared_down", "moe_combine", "final_ln", "mm_head", "sample" };
+                                         "moe_sort", "mm_experts_up", "mm_experts_down", "mm_shared_up", "mm_shared_down", "moe_combine", "final_ln", "mm_head", "sample", "latent_attention_mm" };
 enum { HK_CELLMAP, HK_EMBED, HK_CANON, HK_DQKV, HK_LPREP, HK_UQ, HK_ABSORB, HK_LATTN, HK_UV, HK_AO, HK_QFV, HK_GATES, HK_SCAN, HK_HO, HK_LNRES, HK_UP, HK_POLY, HK_DOWN,
-       HK_ROUTER, HK_ROUTE, HK_SORT, HK_EUP, HK_EDOWN, HK_SUP, HK_SDOWN, HK_COMBINE, HK_FINAL, HK_HEAD, HK_SAMPLE, HK_COUNT };
+       HK_ROUTER, HK_ROUTE, HK_SORT, HK_EUP, HK_EDOWN, HK_SUP, HK_SDOWN, HK_COMBINE, HK_FINAL, HK_HEAD, HK_SAMPLE, HK_LATTN_MM, HK_COUNT };
 const char * pib_hybrid_kind_name(int k) { return k >= 0 && k < HK_COUNT ? HK_NAMES[k] : "?"; }
 
 // fetch and clear the records; returns the count (the stream is synchronised)
@@ -107,6 +110,24 @@ int pib_hybrid_set_slots(pib_context * c, int n_slots) {
 }
 int pib_hybrid_slots_free(const pib_context * c) { return c->hy ? c->hy->slots.n_free() : 0; }
 
+static bool attn_mm_enabled() { static const int on = getenv("PIB_ATTN_MM") ? atoi(getenv("PIB_ATTN_MM")) : 1; return on != 0; }
+
+static int grow_attn_mm(pib_context * c, const pib_hlayer & L, int nq, int NK) {
+    pib_hybrid_ctx * x = c->hy;
+    const size_t R = (size_t) L.kv_rank, RK = R + (size_t) L.rot_dim, NKp = ((size_t) NK + 7) & ~(size_t) 7, rows = (size_t) nq * L.heads;
+    auto grow = [&](void ** p, size_t * cap, size_t need) {
+        if (need <= *cap) return true;
+        cudaStreamSynchronize(c->stream);
+        if (*p) cudaFree(*p);
+        *cap = need + need / 4;
+        if (cudaMalloc(p, *cap) != cudaSuccess) { cudaGetLastError(); *p = nullptr; *cap = 0; return false; }
+        return true;
+    };
+    if (!grow(&x->am_kb, &x->am_kb_cap, NKp * RK * 2) || !grow(&x->am_vt, &x->am_vt_cap, R * NKp * 2) || !grow((void **) &x->am_q, &x->am_q_cap, rows * RK * 4) ||
+        !grow((void **) &x->am_s, &x->am_s_cap, rows * NKp * 4)) { pib_set_error("decode: out of memory for the attention's score rows"); return PIB_ERR_NOMEM; }
+    return PIB_OK;
+}
+
 static void free_scratch(pib_hybrid_ctx * x) {
     for (void * b : { (void *) x->x, (void *) x->h, (void *) x->y, (void *) x->proj, (void *) x->cq, (void *) x->q, (void *) x->qlat, (void *) x->lat, (void *) x->att,
                       (void *) x->rlog, (void *) x->wts, (void *) x->eup, (void *) x->edn, (void *) x->ysh, (void *) x->ids, (void *) x->perm, (void *) x->inv,
@@ -122,6 +143,7 @@ void pib_hybrid_ctx_free(pib_context * c) {
     free_scratch(x);
     if (x->state) cudaFree(x->state);
     if (x->cellmap) cudaFree(x->cellmap);
+    for (void * p : { x->am_kb, x->am_vt, (void *) x->am_q, (void *) x->am_s }) if (p) cudaFree(p);
     for (float * p : x->cache) if (p) cudaFree(p);
     for (float2 * p : x->rope) if (p) cudaFree(p);
     for (int i = 0; i < pib_hybrid_ctx::RING; i++) { if (x->meta_host[i]) cudaFreeHost(x->meta_host[i]); if (x->meta_ev[i]) cudaEventDestroy(x->meta_ev[i]); }
@@ -158,7 +180,16 @@ static int grow_scratch(pib_context * c, int T) {
 }
 
 // ---- the layers -----------------------------------------------------------------------------------------------------------------------
-static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B, const int32_t * B_pos_host) {
+// Attention of a segment of at least MM_ATTN_MIN_LEN tokens runs as matmuls on the tensor cores (served mode, latent rows of at least
+// MM_ATTN_MIN_ROW floats, a multiple of 8), in blocks of MM_ATTN_BLOCK tokens; everything else stays with latent_attn_kernel.
+#define MM_ATTN_MIN_LEN 128
+#define MM_ATTN_MIN_ROW 192
+#define MM_ATTN_BLOCK   256
+struct pib_hseg { int start, len, seq, slot; bool fresh; };
+
+static int grow_attn_mm(pib_context * c, const pib_hlayer & L, int nq, int NK);
+
+static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B, const int32_t * B_pos_host, const std::vector<pib_hseg> & segs) {
     pib_hybrid_ctx *   x  = c->hy;
     const pib_model *  m  = c->model;
     const pib_hybrid * hy = m->hy;
@@ -207,7 +238,24 @@ static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B, cons
                 a.Y = x->qlat; a.ldy = (int64_t) H * R; a.yz = R; a.M = T; a.N = R; a.K = D; a.Z = H; a.exact = exact;
                 RC(HK_ABSORB, 2.0 * Td * H * R * D, wbytes(L.ukT) + 4.0 * Td * H * (D + R), pib_dense_mm(a, st));
             }
-            RC(HK_LATTN, 4.0 * keys * H * (R + rd), 4.0 * keys * (R + rd) + 8.0 * Td * H * R, pib_latent_attention(x->q, x->qlat, L, B, x->rope[L.rope_id], (int) c->n_ctx, cache, row, x->cellmap, (int) c->n_ctx, x->lat, st));
+            const bool mm_ok = !exact && row >= MM_ATTN_MIN_ROW && row % 8 == 0 && attn_mm_enabled();
+            bool any_mm = false, any_simt = false;
+            for (const pib_hseg & g : segs) { if (mm_ok && g.len >= MM_ATTN_MIN_LEN) any_mm = true; else any_simt = true; }
+            if (any_simt)
+                RC(HK_LATTN, 4.0 * keys * H * (R + rd), 4.0 * keys * (R + rd) + 8.0 * Td * H * R,
+                   pib_latent_attention(x->q, x->qlat, L, B, x->rope[L.rope_id], (int) c->n_ctx, cache, row, x->cellmap, (int) c->n_ctx, x->lat, any_mm ? B.mmflag : nullptr, st));
+            for (const pib_hseg & g : segs) {
+                if (!mm_ok || g.len < MM_ATTN_MIN_LEN) continue;
+                for (int o = 0; o < g.len; o += MM_ATTN_BLOCK) {
+                    const int nq = std::min(MM_ATTN_BLOCK, g.len - o), p0 = B_pos_host[g.start + o];
+                    const int j0 = std::max(0, p0 - L.window + 1), NK = p0 + nq - j0;
+                    if ((rc = grow_attn_mm(c, L, nq, NK)) != PIB_OK) return rc;
+                    RC(HK_LATTN_MM, 2.0 * nq * H * (double) NK * (2.0 * R + rd), 2.0 * NK * (2.0 * R + rd) + 8.0 * nq * H * (2.0 * R + rd) + 8.0 * nq * H * (double) NK,
+                       pib_latent_attention_mm(x->q, x->qlat, L, B, x->rope[L.rope_id], cache, row, x->cellmap + (size_t) g.slot * c->n_ctx, g.start + o, nq, j0, NK,
+                                               x->am_kb, x->am_vt, x->am_q, x->am_s, x->lat, st));
+                    nk += 5;
+                }
+            }
             {   // value of head h = W_uv,h (sum_j p_j c_j)
                 pib_mm a;
                 a.W = L.uv->base; a.wtype = L.uv->type; a.ldw = R; a.wz = (int64_t) V * R; a.X = x->lat; a.ldx = (int64_t) H * R; a.xz = R;
@@ -277,8 +325,7 @@ int pib_hybrid_decode_start(pib_context * c, int n_tokens, const int32_t * token
     if (!x->kv_error.empty()) { pib_set_error("decode: %s", x->kv_error.c_str()); return -1; }
     const int T = n_tokens, W = c->n_words;
     // segments: runs of one sequence with consecutive positions
-    struct Seg { int start, len, seq, slot; bool fresh; };
-    std::vector<Seg> segs;
+    std::vector<pib_hseg> segs;
     for (int i = 0; i < T; i++) {
         if (token[i] < 0 || token[i] >= m->n_vocab) { pib_set_error("decode: token id %d out of range", token[i]); return -1; }
         if (n_seq_id[i] != 1) { pib_set_error("decode: a token of a model with per-sequence state belongs to exactly one sequence"); return -1; }
@@ -289,12 +336,12 @@ int pib_hybrid_decode_start(pib_context * c, int n_tokens, const int32_t * token
             if (pos[i] != pos[i - 1] + 1) { pib_set_error("decode: positions of sequence %d are not consecutive", s); return -1; }
             segs.back().len++;
         } else {
-            for (const Seg & g : segs) if (g.seq == s) { pib_set_error("decode: tokens of sequence %d are not next to each other in the batch", s); return -1; }
+            for (const pib_hseg & g : segs) if (g.seq == s) { pib_set_error("decode: tokens of sequence %d are not next to each other in the batch", s); return -1; }
             segs.push_back({ i, 1, s, -1, false });
         }
     }
     int need = 0;
-    for (Seg & g : segs) {
+    for (pib_hseg & g : segs) {
         g.slot = x->slots.find(g.seq);
         const int have = g.slot >= 0 ? x->slots.len[(size_t) g.slot] : 0;
         if (pos[g.start] != have) { pib_set_error("decode: sequence %d continues at position %d, the batch starts at %d", g.seq, have, pos[g.start]); return -1; }
@@ -315,7 +362,7 @@ int pib_hybrid_decode_start(pib_context * c, int n_tokens, const int32_t * token
         return -1;
     }
     cudaStream_t st = c->stream;
-    for (Seg & g : segs) {
+    for (pib_hseg & g : segs) {
         if (g.slot < 0) {
             g.slot = x->slots.acquire(g.seq);
             g.fresh = true;
@@ -324,7 +371,7 @@ int pib_hybrid_decode_start(pib_context * c, int n_tokens, const int32_t * token
         x->slots.len[(size_t) g.slot] += g.len;
     }
     // bookkeeping: [tok | pos | cell | slot | seg] x T, then [seg_start | seg_len | seg_slot] x S
-    const int S = (int) segs.size(), words = 5 * T + 3 * S;
+    const int S = (int) segs.size(), words = 6 * T + 3 * S;
     if (words > x->meta_cap) {
         cudaStreamSynchronize(st);
         for (auto & g : c->graphs) if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
@@ -344,9 +391,9 @@ int pib_hybrid_decode_start(pib_context * c, int n_tokens, const int32_t * token
     cudaEventSynchronize(x->meta_ev[ring]);
     int32_t * mh = x->meta_host[ring];
     for (int sgi = 0; sgi < S; sgi++) {
-        const Seg & g = segs[(size_t) sgi];
-        for (int i = g.start; i < g.start + g.len; i++) { mh[3 * T + i] = g.slot; mh[4 * T + i] = sgi; }
-        mh[5 * T + sgi] = g.start; mh[5 * T + S + sgi] = g.len; mh[5 * T + 2 * S + sgi] = g.slot;
+        const pib_hseg & g = segs[(size_t) sgi];
+        for (int i = g.start; i < g.start + g.len; i++) { mh[3 * T + i] = g.slot; mh[4 * T + i] = sgi; mh[5 * T + i] = g.len >= MM_ATTN_MIN_LEN ? 1 : 0; }
+        mh[6 * T + sgi] = g.start; mh[6 * T + S + sgi] = g.len; mh[6 * T + 2 * S + sgi] = g.slot;
     }
     memcpy(mh, token, (size_t) T * 4);
     memcpy(mh + T, pos, (size_t) T * 4);
@@ -355,7 +402,7 @@ int pib_hybrid_decode_start(pib_context * c, int n_tokens, const int32_t * token
     cudaEventRecord(x->meta_ev[ring], st);
     c->h2d_bytes += (size_t) words * 4;
     const int32_t * md = x->meta_dev;
-    pib_hbatch B = { md, md + T, md + 2 * T, md + 3 * T, md + 4 * T, md + 5 * T, md + 5 * T + S, md + 5 * T + 2 * S, T, S };
+    pib_hbatch B = { md, md + T, md + 2 * T, md + 3 * T, md + 4 * T, md + 5 * T, md + 6 * T, md + 6 * T + S, md + 6 * T + 2 * S, T, S };
     run->in_use = true; run->batch_id = batch_id; run->n_tokens = T; run->failed = false; run->has_walk = false;
     c->tree_pending.n_branches = 0;
     cudaMemcpyAsync(c->cancel_table, c->run_id_host + run->id, sizeof(int), cudaMemcpyHostToDevice, st);
@@ -371,7 +418,7 @@ int pib_hybrid_decode_start(pib_context * c, int n_tokens, const int32_t * token
             cudaGraph_t graph = nullptr;
             bool ok = cudaStreamBeginCapture(st, cudaStreamCaptureModeRelaxed) == cudaSuccess;
             if (ok) {
-                const int rc = run_layers(c, *run, B, pos);
+                const int rc = run_layers(c, *run, B, pos, segs);
                 ok = cudaStreamEndCapture(st, &graph) == cudaSuccess && rc == PIB_OK && graph != nullptr;
             }
             if (ok) ok = cudaGraphInstantiate(&g.exec, graph, 0) == cudaSuccess;
@@ -387,7 +434,7 @@ int pib_hybrid_decode_start(pib_context * c, int n_tokens, const int32_t * token
             done = true;
         }
     }
-    if (!done && run_layers(c, *run, B, pos) != PIB_OK) run->failed = true;
+    if (!done && run_layers(c, *run, B, pos, segs) != PIB_OK) run->failed = true;
     if (!run->failed) {
         cudaMemcpyAsync(run->res_host, run->res_dev, sizeof(pib_row_result) * (size_t) T, cudaMemcpyDeviceToHost, st);
         c->d2h_bytes += sizeof(pib_row_result) * (size_t) T;

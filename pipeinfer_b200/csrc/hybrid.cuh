@@ -94,6 +94,7 @@ pib_weight * pib_dense_upload(int type, const void * host, int64_t N, int64_t K)
 // hybrid_kernels.cu
 struct pib_hbatch {                  // device view of one batch's bookkeeping
     const int32_t * tok, * pos, * cell, * slot, * seg;       // [T]
+    const int32_t * mmflag;                                   // [T] 1: the token's attention runs in the matmul form (long portions, served mode)
     const int32_t * seg_start, * seg_len, * seg_slot;         // [S]
     int T, S;
 };
@@ -104,7 +105,9 @@ int pib_canon_conv(const float * x, const float * w, int taps, const pib_hbatch 
 int pib_latent_prep(const float * proj, int ldp, const pib_hlayer & L, const float * dq_norm, const float * dkv_norm, float eps, const pib_hbatch & b,
                     const float2 * rope, int rope_n_pos, float * cq, float * cache, int cache_row, cudaStream_t st);
 int pib_latent_attention(const float * q, const float * qlat, const pib_hlayer & L, const pib_hbatch & b, const float2 * rope, int rope_n_pos,
-                         const float * cache, int cache_row, const int32_t * cellmap, int n_ctx, float * ctx, cudaStream_t st);
+                         const float * cache, int cache_row, const int32_t * cellmap, int n_ctx, float * ctx, const int32_t * skip, cudaStream_t st);
+int pib_latent_attention_mm(const float * q, const float * qlat, const pib_hlayer & L, const pib_hbatch & b, const float2 * rope, const float * cache, int cache_row,
+                            const int32_t * map, int t0, int nq, int j0, int NK, void * Kb, void * Vt, float * Qc, float * S, float * ctx, cudaStream_t st);
 int pib_hgrn2_gates(float * qfv, int ld, const float * f_bias, const float * lower, int T, int HD, cudaStream_t st);
 int pib_hgrn2_scan(const float * qfv, int ld, const pib_hlayer & L, const pib_hbatch & b, float * state, size_t state_stride, const float * onorm, float eps,
                    float * out, cudaStream_t st);

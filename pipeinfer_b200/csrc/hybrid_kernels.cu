@@ -183,9 +183,11 @@ template <int RPL>
 __global__ void __launch_bounds__(512) latent_attn_kernel(const float * __restrict__ q, int ldq, const float * __restrict__ qlat, int H, int D, int rot_dim, int rot_dims, int R,
                                                           float scale, int window, const float * __restrict__ sink, const int32_t * __restrict__ pos,
                                                           const int32_t * __restrict__ slot, const float2 * __restrict__ rope, const float * __restrict__ cache,
-                                                          int cache_row, const int32_t * __restrict__ cellmap, int n_ctx, int HPB, int KS, float * __restrict__ ctx) {
+                                                          int cache_row, const int32_t * __restrict__ cellmap, int n_ctx, int HPB, int KS, float * __restrict__ ctx,
+                                                          const int32_t * __restrict__ skip) {
     extern __shared__ float sm[];                 // [HPB * KS][R + 2] partial states, then [HPB][rot_dim] rotated queries
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (skip && skip[t]) return;                  // this token's segment goes through the matmul form (pib_latent_attention_mm)
     const int hl = warp / KS, ks = warp % KS, h = blockIdx.y * HPB + hl;
     const int p = pos[t], lo = max(0, p - window + 1);
     float * qr_s = sm + (size_t) HPB * KS * (R + 2) + (size_t) hl * rot_dim;
@@ -254,7 +256,7 @@ __global__ void __launch_bounds__(512) latent_attn_kernel(const float * __restri
 }
 
 int pib_latent_attention(const float * q, const float * qlat, const pib_hlayer & L, const pib_hbatch & b, const float2 * rope, int rope_n_pos,
-                         const float * cache, int cache_row, const int32_t * cellmap, int n_ctx, float * ctx, cudaStream_t st) {
+                         const float * cache, int cache_row, const int32_t * cellmap, int n_ctx, float * ctx, const int32_t * skip, cudaStream_t st) {
     (void) rope_n_pos;
     const int H = L.heads, R = L.kv_rank;
     // few tokens (decoding): one head per CTA and 16 key shares, so that a step still fills some of the machine
@@ -268,13 +270,94 @@ int pib_latent_attention(const float * q, const float * qlat, const pib_hlayer &
 #define LA_GO(RPL) do {                                                                                                            \
         if (smem > 48 * 1024) cudaFuncSetAttribute(latent_attn_kernel<RPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem); \
         latent_attn_kernel<RPL><<<grid, threads, smem, st>>>(q, H * (L.dim + L.rot_dim), qlat, H, L.dim, L.rot_dim, L.rot_dims, R, L.scale, L.window, L.sink, b.pos,  \
-                                                             b.slot, rope, cache, cache_row, cellmap, n_ctx, HPB, KS, ctx);       \
+                                                             b.slot, rope, cache, cache_row, cellmap, n_ctx, HPB, KS, ctx, skip); \
     } while (0)
     if (R <= 128) LA_GO(4); else if (R <= 256) LA_GO(8); else if (R <= 512) LA_GO(16);
     else { pib_set_error("latent attention: kv_rank %d (max 512)", R); return PIB_ERR_UNSUPP; }
 #undef LA_GO
     CKL();
     return PIB_OK;
+}
+
+// ---- latent attention as matmuls (long portions, served mode) ----------------------------------------------------------------------
+// For a block of consecutive tokens of one segment the scores against the block's key range [j0, j0 + NK) are one matmul, the masked
+// softmax with the sink one pass over the score rows, and the weighted sums of latent rows a second matmul.  These kernels prepare the
+// operands: the keys' rows as bfloat16 [NK][R + rot_dim] and, transposed, [R][NKp] (NKp = NK rounded up to 8, the pad zero), and the
+// queries as rows [(token, head)][R + rot_dim] = scale * [W_uk^T q | rotated q part].
+__global__ void __launch_bounds__(128) lat_gather_kernel(const float * __restrict__ cache, int cache_row, const int32_t * __restrict__ map, int j0, int NK, int NKp, int R,
+                                                         int RK, __nv_bfloat16 * __restrict__ Kb, __nv_bfloat16 * __restrict__ Vt) {
+    const int j = blockIdx.x;
+    if (j < NK) {
+        const float * row = cache + (size_t) map[j0 + j] * cache_row;
+        for (int i = threadIdx.x; i < RK; i += blockDim.x) {
+            const __nv_bfloat16 v = __float2bfloat16_rn(row[i]);
+            Kb[(size_t) j * RK + i] = v;
+            if (i < R) Vt[(size_t) i * NKp + j] = v;
+        }
+    } else {
+        for (int i = threadIdx.x; i < R; i += blockDim.x) Vt[(size_t) i * NKp + j] = __float2bfloat16_rn(0.f);
+    }
+}
+__global__ void __launch_bounds__(128) lat_qcat_kernel(const float * __restrict__ q, int ldq, const float * __restrict__ qlat, int H, int D, int rot_dim, int rot_dims, int R,
+                                                       float scale, const int32_t * __restrict__ pos, const float2 * __restrict__ rope, int t0, float * __restrict__ Qc) {
+    const int t = t0 + blockIdx.x, h = blockIdx.y, RK = R + rot_dim;
+    float *       out = Qc + ((size_t) blockIdx.x * H + h) * RK;
+    const float * ql = qlat + ((size_t) t * H + h) * R;
+    for (int i = threadIdx.x; i < R; i += blockDim.x) out[i] = ql[i] * scale;
+    const float *  qr = q + (size_t) t * ldq + (size_t) h * (D + rot_dim) + D;
+    const int      half = rot_dims / 2;
+    const float2 * cs = rope + (size_t) pos[t] * half;
+    for (int i = threadIdx.x; i < rot_dim; i += blockDim.x) {
+        float v;
+        if (i < half)          v = qr[i] * cs[i].x - qr[i + half] * cs[i].y;
+        else if (i < rot_dims) v = qr[i] * cs[i - half].x + qr[i - half] * cs[i - half].y;
+        else                   v = qr[i];
+        out[R + i] = v * scale;
+    }
+}
+// one score row per (token, head), in place: keys outside [p - window + 1, p] and the pad get weight 0, the sink one share of the denominator
+__global__ void __launch_bounds__(256) lat_softmax_kernel(float * __restrict__ S, int NKp, int NK, int j0, int window, const int32_t * __restrict__ pos, int t0, int H,
+                                                          const float * __restrict__ sink) {
+    __shared__ float red[32];
+    const int row = blockIdx.x, t = t0 + row / H, h = row % H, p = pos[t];
+    float *   s = S + (size_t) row * NKp;
+    const int lo = max(0, p - window + 1) - j0, hi = p - j0;            // valid columns [lo, hi]
+    const float sk = sink[h];
+    float m = sk;
+    for (int j = lo + (int) threadIdx.x; j <= hi; j += blockDim.x) m = fmaxf(m, s[j]);
+    m = warp_max(m);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+    __syncthreads();
+    for (int i = 0; i < (int) (blockDim.x >> 5); i++) m = fmaxf(m, red[i]);
+    float sum = 0.f;
+    for (int j = threadIdx.x; j < NKp; j += blockDim.x) {
+        const float e = (j >= lo && j <= hi) ? expf(s[j] - m) : 0.f;
+        s[j] = e;
+        sum += e;
+    }
+    const float inv = 1.0f / (block_sum(sum, red) + expf(sk - m));
+    for (int j = lo + (int) threadIdx.x; j <= hi; j += blockDim.x) s[j] *= inv;
+    (void) NK;
+}
+
+// the block of `nq` tokens starting at batch row t0 (positions p0 ..), keys [j0, j0 + NK): ctx rows [(token, head)][R] of those tokens
+int pib_latent_attention_mm(const float * q, const float * qlat, const pib_hlayer & L, const pib_hbatch & b, const float2 * rope, const float * cache, int cache_row,
+                            const int32_t * map, int t0, int nq, int j0, int NK, void * Kb, void * Vt, float * Qc, float * S, float * ctx, cudaStream_t st) {
+    const int H = L.heads, R = L.kv_rank, RK = R + L.rot_dim, NKp = (NK + 7) & ~7;
+    lat_gather_kernel<<<NKp, 128, 0, st>>>(cache, cache_row, map, j0, NK, NKp, R, RK, (__nv_bfloat16 *) Kb, (__nv_bfloat16 *) Vt);
+    CKL();
+    lat_qcat_kernel<<<dim3((unsigned) nq, (unsigned) H), 128, 0, st>>>(q, H * (L.dim + L.rot_dim), qlat, H, L.dim, L.rot_dim, L.rot_dims, R, L.scale, b.pos, rope, t0, Qc);
+    CKL();
+    pib_mm a;
+    a.W = Kb; a.wtype = PIB_TYPE_BF16; a.ldw = RK; a.X = Qc; a.ldx = RK; a.Y = S; a.ldy = NKp; a.M = nq * H; a.N = NK; a.K = RK;
+    int rc = pib_dense_mm(a, st);
+    if (rc != PIB_OK) return rc;
+    lat_softmax_kernel<<<nq * H, 256, 0, st>>>(S, NKp, NK, j0, L.window, b.pos, t0, H, L.sink);
+    CKL();
+    pib_mm v;
+    v.W = Vt; v.wtype = PIB_TYPE_BF16; v.ldw = NKp; v.X = S; v.ldx = NKp; v.Y = ctx + (size_t) t0 * H * R; v.ldy = R; v.M = nq * H; v.N = R; v.K = NKp;
+    return pib_dense_mm(v, st);
 }
 
 // ---- HGRN2 ----------------------------------------------------------------------------------------------------------------------

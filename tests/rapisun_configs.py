@@ -72,4 +72,12 @@ def partial_rotation():
     return model(40, 50, [("latent_attention", latent(2, 8, 12, 8, 24, 16, 6, rot_dims=8), dense(40))], taps=5)
 
 
-CONFIGS = {f.__name__: f for f in (mixed_small, attention_only, recurrent_only, experts_only, ones, far_keys, partial_rotation)}
+def wide_latent():
+    """latent rows of 192 floats: long portions of such a layer take the tensor-core (matmul) form of the attention in served mode.
+    No routed experts: the test compares bfloat16 runs with each other, and a router's near tie would turn rounding into a discrete change"""
+    a = latent(2, 32, 16, 24, 176, 48, 150, base=20000.0)
+    return model(64, 160, [("latent_attention", a, dense(72)), ("hgrn2", hgrn2(2, 16, 16), None),
+                           ("latent_attention", dict(a, kv_from=0, mask={"size": 37}), dense(48))], taps=3)
+
+
+CONFIGS = {f.__name__: f for f in (wide_latent, mixed_small, attention_only, recurrent_only, experts_only, ones, far_keys, partial_rotation)}

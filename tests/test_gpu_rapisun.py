@@ -248,6 +248,36 @@ def test_long_decoding(tmp_path):
     assert e.max() < TOL32 and e[-20:].max() < TOL32
 
 
+def test_long_portions_take_the_matmul_attention(tmp_path):
+    """served mode: portions of 128 tokens and more of a layer with wide latent rows run their attention as tensor-core matmuls (scores,
+    masked softmax with the sink, weighted sums); shorter portions and decoded tokens stay with the per-token kernel.  Both against the
+    oracle, against each other, and mixed in one batch"""
+    cfg = CONFIGS["wide_latent"]()
+    W = O.random_weights(cfg, 23)
+    for k in W:
+        if k.endswith("sink"):
+            W[k] = O.bf16_round(W[k] - 4.0)
+    toks, other = tokens(cfg, 450, 10), tokens(cfg, 60, 11)
+    ref, ref_o = oracle_logits(cfg, W, toks), oracle_logits(cfg, W, other)
+    s = Served(tmp_path, cfg, W, float32=False, n_ctx=1600)
+    whole = s.feed(0, toks, [])                                            # one portion of 450: blocks of 256 + 194, windows of 150 and 37 inside
+    small = s.feed(1, toks, range(100, 450, 100))                          # portions of 100: the per-token kernel
+    cut = s.feed(2, toks, [130, 131, 300, 449])                            # 130 (matmul) + 1 + 169 (matmul) + 149 (matmul) + 1
+    assert row_err(whole, ref).max() < TOL16 and row_err(small, ref).max() < TOL16 and row_err(cut, ref).max() < TOL16
+    assert row_err(whole, small).max() < TOL16 / 2 and row_err(cut, small).max() < TOL16 / 2
+    # a long portion beside a short one and a decoded token in ONE batch
+    for r in range(3):
+        s.end(r)
+    a = s.step([(3, toks[:200]), (4, other[:59])])
+    b = s.step([(4, other[59:]), (3, toks[200:])])
+    assert row_err(np.concatenate([a[3], b[3]]), ref).max() < TOL16
+    assert row_err(np.concatenate([a[4], b[4]]), ref_o).max() < TOL16
+    s.close()
+    s = Served(tmp_path, cfg, W, float32=True, n_ctx=600)                  # float32 contexts never take it
+    assert row_err(s.feed(0, toks, []), ref).max() < TOL32
+    s.close()
+
+
 def test_decode_steps_around_growing_prompts(tmp_path):
     """single-token steps are replayed from captured graphs; a later, longer prompt makes the context grow its buffers (logits rows of a
     run slot, work buffers), and the steps after it must not run on the old ones"""
