@@ -123,7 +123,7 @@ template <> struct wvec<float> {
 };
 
 template <typename WT, bool ROUND, int EPI, int B>
-__global__ void __launch_bounds__(256) mv_rows_kernel(mm_dev a) {
+__global__ void __launch_bounds__(256) mv_rows_kernel(mm_dev a, bool xvec) {
     const int z = blockIdx.z;
     int row0 = 0, row1 = a.M;
     if (a.zrange) { row0 = a.zrange[z]; row1 = a.zrange[z + 1]; }
@@ -151,12 +151,16 @@ __global__ void __launch_bounds__(256) mv_rows_kernel(mm_dev a) {
         wvec<WT>::load(W + k, w);
 #pragma unroll
         for (int b = 0; b < B; b++) {
+            float xv[V];
+            if (xvec) {             // rows of X start on 16-byte boundaries (checked on the host): 128-bit loads
 #pragma unroll
-            for (int i = 0; i < V; i++) {
-                float xv = xr[b][k + i];
-                if (ROUND) xv = round_bf16(xv);
-                acc[b] = fmaf(xv, w[i], acc[b]);
+                for (int i = 0; i < V; i += 4) *reinterpret_cast<float4 *>(xv + i) = *reinterpret_cast<const float4 *>(xr[b] + k + i);
+            } else {
+#pragma unroll
+                for (int i = 0; i < V; i++) xv[i] = xr[b][k + i];
             }
+#pragma unroll
+            for (int i = 0; i < V; i++) acc[b] = fmaf(ROUND ? round_bf16(xv[i]) : xv[i], w[i], acc[b]);
         }
     }
     for (int k = Kv + lane; k < a.K; k += 32) {
@@ -182,11 +186,12 @@ static int launch_mm(const pib_mm & a, const mm_dev & d, cudaStream_t st) {
     // few rows in all (with zrange: no problem z can own more than the total): a warp per weight row; problems without rows leave at once
     if (a.M <= MV_MAXB && vec_ok) {
         dim3 grid((unsigned) ((a.N + 7) / 8), 1, (unsigned) a.Z);
-        if (a.M == 1)      mv_rows_kernel<WT, ROUND, EPI, 1><<<grid, 256, 0, st>>>(d);
-        else if (a.M == 2) mv_rows_kernel<WT, ROUND, EPI, 2><<<grid, 256, 0, st>>>(d);
-        else if (a.M <= 4) mv_rows_kernel<WT, ROUND, EPI, 4><<<grid, 256, 0, st>>>(d);
-        else if (a.M <= 8) mv_rows_kernel<WT, ROUND, EPI, 8><<<grid, 256, 0, st>>>(d);
-        else               mv_rows_kernel<WT, ROUND, EPI, MV_MAXB><<<grid, 256, 0, st>>>(d);
+        const bool xvec = a.ldx % 4 == 0 && a.xz % 4 == 0 && ((uintptr_t) a.X & 15) == 0;
+        if (a.M == 1)      mv_rows_kernel<WT, ROUND, EPI, 1><<<grid, 256, 0, st>>>(d, xvec);
+        else if (a.M == 2) mv_rows_kernel<WT, ROUND, EPI, 2><<<grid, 256, 0, st>>>(d, xvec);
+        else if (a.M <= 4) mv_rows_kernel<WT, ROUND, EPI, 4><<<grid, 256, 0, st>>>(d, xvec);
+        else if (a.M <= 8) mv_rows_kernel<WT, ROUND, EPI, 8><<<grid, 256, 0, st>>>(d, xvec);
+        else               mv_rows_kernel<WT, ROUND, EPI, MV_MAXB><<<grid, 256, 0, st>>>(d, xvec);
     } else {
         dim3 grid((unsigned) ((a.M + MM_BM - 1) / MM_BM), (unsigned) ((a.N + MM_BN - 1) / MM_BN), (unsigned) a.Z);
         mm_tile_kernel<WT, ROUND, EPI><<<grid, 256, 0, st>>>(d);
