@@ -247,6 +247,20 @@ int  llama_pib_pipe_shutdown(struct llama_context * ctx);
 int  llama_pib_set_priority(struct llama_context * ctx, int high);
 /* context with an explicit sequence-id capacity (the reference sizes std::set on demand) */
 struct llama_context * llama_pib_new_context(struct llama_model * model, uint32_t n_ctx, int32_t max_seq_ids);
+
+/* ---- layer-list models: a folder with config.json + model.safetensors instead of a GGUF file (llama_load_model_from_file accepts
+ * the folder too and takes the compute type from PIB_DTYPE).  float32 != 0: weights widened once, everything in true 32-bit;
+ * 0: bfloat16 matmul operands, fp32 accumulation.  A context of such a model keeps one state slot per live sequence beside its KV
+ * cells: a token belongs to exactly one sequence, a sequence's tokens are neighbours in a batch and continue its positions;
+ * llama_kv_cache_seq_rm(ctx, seq, -1, -1) / _clear / _seq_keep give cells and slot back; copies and partial removals are refused. */
+struct llama_model * llama_pib_load_model_dir(const char * path, int float32);
+struct llama_model * llama_pib_synthetic_config_model(const char * config_json, uint64_t seed, int float32);   /* random weights for a configuration */
+int  llama_pib_set_state_slots(struct llama_context * ctx, int n_slots);      /* before the first decode; default min(max_seq_ids, 8) or PIB_STATE_SLOTS */
+int  llama_pib_state_slots_free(const struct llama_context * ctx);
+/* per-launch profile of such a context while llama_pib_profile_layer(ctx, >= 0) is on: kind (llama_pib_hybrid_kind_name), milliseconds,
+ * floating-point operations, algorithmic bytes; returns the count and clears the records */
+int  llama_pib_hybrid_profile_read(struct llama_context * ctx, int32_t * kind, float * ms, double * flops, double * bytes, int cap);
+const char * llama_pib_hybrid_kind_name(int kind);
 /* KV bookkeeping probes for parity tests: head / used / n, cell positions and sequence bitset rows, host mirror (0)
  * or device replica (1) */
 int  llama_pib_kv_state(struct llama_context * ctx, int from_device, int32_t * scalars3, int32_t * pos, uint32_t * bits);

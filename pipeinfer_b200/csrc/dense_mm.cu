@@ -33,6 +33,8 @@ struct mm_dev {
 
 template <typename WT, bool ROUND, int EPI>
 __global__ void __launch_bounds__(256) mm_tile_kernel(mm_dev a) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
     const int z = blockIdx.z;
     int row0 = 0, row1 = a.M;
     if (a.zrange) { row0 = a.zrange[z]; row1 = a.zrange[z + 1]; }
@@ -124,6 +126,8 @@ template <> struct wvec<float> {
 
 template <typename WT, bool ROUND, int EPI, int B>
 __global__ void __launch_bounds__(256) mv_rows_kernel(mm_dev a, bool xvec) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
     const int z = blockIdx.z;
     int row0 = 0, row1 = a.M;
     if (a.zrange) { row0 = a.zrange[z]; row1 = a.zrange[z + 1]; }
@@ -187,14 +191,14 @@ static int launch_mm(const pib_mm & a, const mm_dev & d, cudaStream_t st) {
     if (a.M <= MV_MAXB && vec_ok) {
         dim3 grid((unsigned) ((a.N + 7) / 8), 1, (unsigned) a.Z);
         const bool xvec = a.ldx % 4 == 0 && a.xz % 4 == 0 && ((uintptr_t) a.X & 15) == 0;
-        if (a.M == 1)      mv_rows_kernel<WT, ROUND, EPI, 1><<<grid, 256, 0, st>>>(d, xvec);
-        else if (a.M == 2) mv_rows_kernel<WT, ROUND, EPI, 2><<<grid, 256, 0, st>>>(d, xvec);
-        else if (a.M <= 4) mv_rows_kernel<WT, ROUND, EPI, 4><<<grid, 256, 0, st>>>(d, xvec);
-        else if (a.M <= 8) mv_rows_kernel<WT, ROUND, EPI, 8><<<grid, 256, 0, st>>>(d, xvec);
-        else               mv_rows_kernel<WT, ROUND, EPI, MV_MAXB><<<grid, 256, 0, st>>>(d, xvec);
+        if (a.M == 1)      pib_launch(mv_rows_kernel<WT, ROUND, EPI, 1>, dim3(grid), dim3(256), (size_t) (0), st, d, xvec);
+        else if (a.M == 2) pib_launch(mv_rows_kernel<WT, ROUND, EPI, 2>, dim3(grid), dim3(256), (size_t) (0), st, d, xvec);
+        else if (a.M <= 4) pib_launch(mv_rows_kernel<WT, ROUND, EPI, 4>, dim3(grid), dim3(256), (size_t) (0), st, d, xvec);
+        else if (a.M <= 8) pib_launch(mv_rows_kernel<WT, ROUND, EPI, 8>, dim3(grid), dim3(256), (size_t) (0), st, d, xvec);
+        else               pib_launch(mv_rows_kernel<WT, ROUND, EPI, MV_MAXB>, dim3(grid), dim3(256), (size_t) (0), st, d, xvec);
     } else {
         dim3 grid((unsigned) ((a.M + MM_BM - 1) / MM_BM), (unsigned) ((a.N + MM_BN - 1) / MM_BN), (unsigned) a.Z);
-        mm_tile_kernel<WT, ROUND, EPI><<<grid, 256, 0, st>>>(d);
+        pib_launch(mm_tile_kernel<WT, ROUND, EPI>, dim3(grid), dim3(256), (size_t) (0), st, d);
     }
     PIB_CHECK(cudaGetLastError());
     return PIB_OK;

@@ -67,6 +67,8 @@ __device__ __forceinline__ void dt_commit(uint32_t bar) {
 // ---- fp32 rows -> bfloat16 rows [Zs][M][Kp] (Kp = K rounded up to 8, the tail zero), gathered through xrows ---------------------------
 __global__ void dense_cast_kernel(const float * __restrict__ X, int64_t ldx, int64_t xz, const int32_t * __restrict__ xrows, int xdiv, int M, int K, int Kp,
                                   __nv_bfloat16 * __restrict__ out) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
     const int m = blockIdx.x, z = blockIdx.y;
     const float * src = X + (size_t) z * xz + (size_t) (xrows ? xrows[m] / xdiv : m) * ldx;
     __nv_bfloat16 * dst = out + ((size_t) z * M + m) * Kp;
@@ -87,6 +89,8 @@ template <int NB, int EPI>
 __global__ void __launch_bounds__(DT_THREADS)
 dense_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap, int M, int N, int K, const int32_t * __restrict__ zrange,
                 int x_has_z, float * __restrict__ Y, int64_t ldy, int64_t yz, int * __restrict__ err) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
     const int z = blockIdx.z;
     int row0 = 0, row1 = M;
     if (zrange) { row0 = zrange[z]; row1 = zrange[z + 1]; }
@@ -248,8 +252,8 @@ static int dt_launch(const pib_mm & a, const CUtensorMap & wmap, const CUtensorM
         configured = true;
     }
     dim3 grid((unsigned) ((a.N + DT_BM - 1) / DT_BM), (unsigned) ((a.M + NB - 1) / NB), (unsigned) a.Z);
-    if (a.epi == PIB_EPI_RELU2) dense_tc_kernel<NB, PIB_EPI_RELU2><<<grid, DT_THREADS, C::SMEM, st>>>(wmap, xmap, a.M, a.N, a.K, a.zrange, x_has_z, a.Y, a.ldy, a.yz, err);
-    else                        dense_tc_kernel<NB, PIB_EPI_NONE><<<grid, DT_THREADS, C::SMEM, st>>>(wmap, xmap, a.M, a.N, a.K, a.zrange, x_has_z, a.Y, a.ldy, a.yz, err);
+    if (a.epi == PIB_EPI_RELU2) pib_launch(dense_tc_kernel<NB, PIB_EPI_RELU2>, dim3(grid), dim3(DT_THREADS), (size_t) (C::SMEM), st, wmap, xmap, a.M, a.N, a.K, a.zrange, x_has_z, a.Y, a.ldy, a.yz, err);
+    else                        pib_launch(dense_tc_kernel<NB, PIB_EPI_NONE>, dim3(grid), dim3(DT_THREADS), (size_t) (C::SMEM), st, wmap, xmap, a.M, a.N, a.K, a.zrange, x_has_z, a.Y, a.ldy, a.yz, err);
     PIB_CHECK(cudaGetLastError());
     return PIB_OK;
 }
@@ -266,7 +270,7 @@ int pib_dense_mm_tc(const pib_mm & a, cudaStream_t st) {
     const int  Zs = grouped ? 1 : a.Z;
     dt_scratch * sc = dt_scratch_of(st, (size_t) Zs * a.M * Kp * 2 + 256);
     if (!sc || !sc->xs) return PIB_ERR_UNSUPP;
-    dense_cast_kernel<<<dim3((unsigned) a.M, (unsigned) Zs), 128, 0, st>>>(a.X, a.ldx, a.xz, a.xrows, a.xdiv < 1 ? 1 : a.xdiv, a.M, a.K, Kp, sc->xs);
+    pib_launch(dense_cast_kernel, dim3(dim3((unsigned) a.M, (unsigned) Zs)), dim3(128), (size_t) (0), st, a.X, a.ldx, a.xz, a.xrows, a.xdiv < 1 ? 1 : a.xdiv, a.M, a.K, Kp, sc->xs);
     PIB_CHECK(cudaGetLastError());
     // the token tile: as wide as the rows of one problem allow (grouped problems: the average share of an expert)
     const int per = grouped ? (a.M + a.Z - 1) / a.Z : a.M;

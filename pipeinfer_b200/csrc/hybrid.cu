@@ -434,7 +434,12 @@ int pib_hybrid_decode_start(pib_context * c, int n_tokens, const int32_t * token
             done = true;
         }
     }
-    if (!done && run_layers(c, *run, B, pos, segs) != PIB_OK) run->failed = true;
+    if (!done) {
+        // event-timed launches run in plain stream order: with programmatic dependent launch a kernel starts before the event in front of it fires
+        if (c->prof_layer >= 0) pib_pdl_suspend(true);
+        if (run_layers(c, *run, B, pos, segs) != PIB_OK) run->failed = true;
+        if (c->prof_layer >= 0) pib_pdl_suspend(false);
+    }
     if (!run->failed) {
         cudaMemcpyAsync(run->res_host, run->res_dev, sizeof(pib_row_result) * (size_t) T, cudaMemcpyDeviceToHost, st);
         c->d2h_bytes += sizeof(pib_row_result) * (size_t) T;

@@ -42,6 +42,8 @@ __device__ __forceinline__ void ln_row(const float * row, const float * __restri
 }
 
 __global__ void __launch_bounds__(256) layer_norm_kernel(const float * __restrict__ in, const float * __restrict__ w, float eps, int W, float * out, int accumulate) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
     extern __shared__ float srow[];
     __shared__ float red[32];
     const float * r = in + (size_t) blockIdx.x * W;
@@ -53,6 +55,8 @@ __global__ void __launch_bounds__(256) layer_norm_kernel(const float * __restric
 template <typename WT>
 __global__ void __launch_bounds__(256) embed_ln_kernel(const WT * __restrict__ embd, const int32_t * __restrict__ tok, const float * __restrict__ w, float eps, int W,
                                                        float * __restrict__ x) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
     extern __shared__ float srow[];
     __shared__ float red[32];
     const WT * r = embd + (size_t) tok[blockIdx.x] * W;
@@ -62,14 +66,14 @@ __global__ void __launch_bounds__(256) embed_ln_kernel(const WT * __restrict__ e
 }
 
 int pib_embed_ln(const pib_weight * embd, const int32_t * tok, const float * w, float eps, int T, int W, float * x, cudaStream_t st) {
-    if (embd->type == PIB_TYPE_BF16) embed_ln_kernel<__nv_bfloat16><<<T, 256, (size_t) W * 4, st>>>((const __nv_bfloat16 *) embd->base, tok, w, eps, W, x);
-    else                             embed_ln_kernel<float><<<T, 256, (size_t) W * 4, st>>>((const float *) embd->base, tok, w, eps, W, x);
+    if (embd->type == PIB_TYPE_BF16) pib_launch(embed_ln_kernel<__nv_bfloat16>, dim3(T), dim3(256), (size_t) ((size_t) W * 4), st, (const __nv_bfloat16 *) embd->base, tok, w, eps, W, x);
+    else                             pib_launch(embed_ln_kernel<float>, dim3(T), dim3(256), (size_t) ((size_t) W * 4), st, (const float *) embd->base, tok, w, eps, W, x);
     CKL();
     return PIB_OK;
 }
 
 int pib_layer_norm(const float * in, const float * w, float eps, int T, int W, float * out, int accumulate, cudaStream_t st) {
-    layer_norm_kernel<<<T, 256, (size_t) W * 4, st>>>(in, w, eps, W, out, accumulate);
+    pib_launch(layer_norm_kernel, dim3(T), dim3(256), (size_t) ((size_t) W * 4), st, in, w, eps, W, out, accumulate);
     CKL();
     return PIB_OK;
 }
@@ -80,6 +84,8 @@ int pib_layer_norm(const float * in, const float * w, float eps, int T, int W, f
 __global__ void __launch_bounds__(256) canon_kernel(const float * __restrict__ x, const float * __restrict__ w, int taps, const int32_t * __restrict__ seg,
                                                     const int32_t * __restrict__ seg_start, const int32_t * __restrict__ seg_slot,
                                                     const float * __restrict__ state, size_t state_stride, size_t tail_off, int W, float * __restrict__ h) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
     const int t = blockIdx.x, sg = seg[t], s0 = seg_start[sg];
     const float * tail = state + (size_t) seg_slot[sg] * state_stride + tail_off;
     for (int c = threadIdx.x; c < W; c += blockDim.x) {
@@ -96,6 +102,8 @@ __global__ void __launch_bounds__(256) canon_kernel(const float * __restrict__ x
 // after canon_kernel: the last taps-1 inputs of every segment become its slot's tail (old tail rows move up when the segment is shorter)
 __global__ void __launch_bounds__(256) canon_tail_kernel(const float * __restrict__ x, int taps, const int32_t * __restrict__ seg_start, const int32_t * __restrict__ seg_len,
                                                          const int32_t * __restrict__ seg_slot, float * __restrict__ state, size_t state_stride, size_t tail_off, int W) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
     const int sg = blockIdx.x, s0 = seg_start[sg], s1 = s0 + seg_len[sg];
     float * tail = state + (size_t) seg_slot[sg] * state_stride + tail_off;
     for (int c = threadIdx.x; c < W; c += blockDim.x) {
@@ -115,20 +123,22 @@ __global__ void __launch_bounds__(256) canon_tail_kernel(const float * __restric
 int pib_canon_conv(const float * x, const float * w, int taps, const pib_hbatch & b, float * state, size_t state_stride, size_t tail_off, int W, float * h,
                    cudaStream_t st) {
     if (taps > CANON_MAX_TAPS) { pib_set_error("convolution: %d taps (max %d)", taps, CANON_MAX_TAPS); return PIB_ERR_UNSUPP; }
-    canon_kernel<<<b.T, 256, 0, st>>>(x, w, taps, b.seg, b.seg_start, b.seg_slot, state, state_stride, tail_off, W, h);
+    pib_launch(canon_kernel, dim3(b.T), dim3(256), (size_t) (0), st, x, w, taps, b.seg, b.seg_start, b.seg_slot, state, state_stride, tail_off, W, h);
     CKL();
-    if (taps > 1) { canon_tail_kernel<<<b.S, 256, 0, st>>>(x, taps, b.seg_start, b.seg_len, b.seg_slot, state, state_stride, tail_off, W); CKL(); }
+    if (taps > 1) { pib_launch(canon_tail_kernel, dim3(b.S), dim3(256), (size_t) (0), st, x, taps, b.seg_start, b.seg_len, b.seg_slot, state, state_stride, tail_off, W); CKL(); }
     return PIB_OK;
 }
 
 // ---- position -> cell table of each state slot -----------------------------------------------------------------------------------
 __global__ void cellmap_kernel(int32_t * __restrict__ cellmap, int n_ctx, const int32_t * __restrict__ pos, const int32_t * __restrict__ cell,
                                const int32_t * __restrict__ slot, int T) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
     const int t = blockIdx.x * blockDim.x + threadIdx.x;
     if (t < T) cellmap[(size_t) slot[t] * n_ctx + pos[t]] = cell[t];
 }
 int pib_cellmap_set(int32_t * cellmap, int n_ctx, const pib_hbatch & b, cudaStream_t st) {
-    cellmap_kernel<<<(b.T + 255) / 256, 256, 0, st>>>(cellmap, n_ctx, b.pos, b.cell, b.slot, b.T);
+    pib_launch(cellmap_kernel, dim3((b.T + 255) / 256), dim3(256), (size_t) (0), st, cellmap, n_ctx, b.pos, b.cell, b.slot, b.T);
     CKL();
     return PIB_OK;
 }
@@ -140,6 +150,8 @@ __global__ void __launch_bounds__(128) latent_prep_kernel(const float * __restri
                                                           const float * __restrict__ dq_norm, const float * __restrict__ dkv_norm, float eps,
                                                           const int32_t * __restrict__ pos, const int32_t * __restrict__ cell,
                                                           const float2 * __restrict__ rope, float * __restrict__ cq, float * __restrict__ cache, int cache_row) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
     __shared__ float red[32];
     const int     t = blockIdx.x;
     const float * p = proj + (size_t) t * ldp;
@@ -169,7 +181,7 @@ __global__ void __launch_bounds__(128) latent_prep_kernel(const float * __restri
 int pib_latent_prep(const float * proj, int ldp, const pib_hlayer & L, const float * dq_norm, const float * dkv_norm, float eps, const pib_hbatch & b,
                     const float2 * rope, int rope_n_pos, float * cq, float * cache, int cache_row, cudaStream_t st) {
     (void) rope_n_pos;
-    latent_prep_kernel<<<b.T, 128, 0, st>>>(proj, ldp, L.q_rank, L.kv_rank, L.rot_dim, L.rot_dims, dq_norm, dkv_norm, eps, b.pos, b.cell, rope, cq, cache, cache_row);
+    pib_launch(latent_prep_kernel, dim3(b.T), dim3(128), (size_t) (0), st, proj, ldp, L.q_rank, L.kv_rank, L.rot_dim, L.rot_dims, dq_norm, dkv_norm, eps, b.pos, b.cell, rope, cq, cache, cache_row);
     CKL();
     return PIB_OK;
 }
@@ -185,6 +197,8 @@ __global__ void __launch_bounds__(512) latent_attn_kernel(const float * __restri
                                                           const int32_t * __restrict__ slot, const float2 * __restrict__ rope, const float * __restrict__ cache,
                                                           int cache_row, const int32_t * __restrict__ cellmap, int n_ctx, int HPB, int KS, float * __restrict__ ctx,
                                                           const int32_t * __restrict__ skip) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
     extern __shared__ float sm[];                 // [HPB * KS][R + 2] partial states, then [HPB][rot_dim] rotated queries
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (skip && skip[t]) return;                  // this token's segment goes through the matmul form (pib_latent_attention_mm)
@@ -269,7 +283,7 @@ int pib_latent_attention(const float * q, const float * qlat, const pib_hlayer &
     const int threads = HPB * KS * 32;
 #define LA_GO(RPL) do {                                                                                                            \
         if (smem > 48 * 1024) cudaFuncSetAttribute(latent_attn_kernel<RPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem); \
-        latent_attn_kernel<RPL><<<grid, threads, smem, st>>>(q, H * (L.dim + L.rot_dim), qlat, H, L.dim, L.rot_dim, L.rot_dims, R, L.scale, L.window, L.sink, b.pos,  \
+        pib_launch(latent_attn_kernel<RPL>, dim3(grid), dim3(threads), (size_t) (smem), st, q, H * (L.dim + L.rot_dim), qlat, H, L.dim, L.rot_dim, L.rot_dims, R, L.scale, L.window, L.sink, b.pos,  \
                                                              b.slot, rope, cache, cache_row, cellmap, n_ctx, HPB, KS, ctx, skip); \
     } while (0)
     if (R <= 128) LA_GO(4); else if (R <= 256) LA_GO(8); else if (R <= 512) LA_GO(16);
@@ -286,6 +300,8 @@ int pib_latent_attention(const float * q, const float * qlat, const pib_hlayer &
 // queries as rows [(token, head)][R + rot_dim] = scale * [W_uk^T q | rotated q part].
 __global__ void __launch_bounds__(128) lat_gather_kernel(const float * __restrict__ cache, int cache_row, const int32_t * __restrict__ map, int j0, int NK, int NKp, int R,
                                                          int RK, __nv_bfloat16 * __restrict__ Kb, __nv_bfloat16 * __restrict__ Vt) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
     const int j = blockIdx.x;
     if (j < NK) {
         const float * row = cache + (size_t) map[j0 + j] * cache_row;
@@ -300,6 +316,8 @@ __global__ void __launch_bounds__(128) lat_gather_kernel(const float * __restric
 }
 __global__ void __launch_bounds__(128) lat_qcat_kernel(const float * __restrict__ q, int ldq, const float * __restrict__ qlat, int H, int D, int rot_dim, int rot_dims, int R,
                                                        float scale, const int32_t * __restrict__ pos, const float2 * __restrict__ rope, int t0, float * __restrict__ Qc) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
     const int t = t0 + blockIdx.x, h = blockIdx.y, RK = R + rot_dim;
     float *       out = Qc + ((size_t) blockIdx.x * H + h) * RK;
     const float * ql = qlat + ((size_t) t * H + h) * R;
@@ -318,6 +336,8 @@ __global__ void __launch_bounds__(128) lat_qcat_kernel(const float * __restrict_
 // one score row per (token, head), in place: keys outside [p - window + 1, p] and the pad get weight 0, the sink one share of the denominator
 __global__ void __launch_bounds__(256) lat_softmax_kernel(float * __restrict__ S, int NKp, int NK, int j0, int window, const int32_t * __restrict__ pos, int t0, int H,
                                                           const float * __restrict__ sink) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
     __shared__ float red[32];
     const int row = blockIdx.x, t = t0 + row / H, h = row % H, p = pos[t];
     float *   s = S + (size_t) row * NKp;
@@ -345,15 +365,15 @@ __global__ void __launch_bounds__(256) lat_softmax_kernel(float * __restrict__ S
 int pib_latent_attention_mm(const float * q, const float * qlat, const pib_hlayer & L, const pib_hbatch & b, const float2 * rope, const float * cache, int cache_row,
                             const int32_t * map, int t0, int nq, int j0, int NK, void * Kb, void * Vt, float * Qc, float * S, float * ctx, cudaStream_t st) {
     const int H = L.heads, R = L.kv_rank, RK = R + L.rot_dim, NKp = (NK + 7) & ~7;
-    lat_gather_kernel<<<NKp, 128, 0, st>>>(cache, cache_row, map, j0, NK, NKp, R, RK, (__nv_bfloat16 *) Kb, (__nv_bfloat16 *) Vt);
+    pib_launch(lat_gather_kernel, dim3(NKp), dim3(128), (size_t) (0), st, cache, cache_row, map, j0, NK, NKp, R, RK, (__nv_bfloat16 *) Kb, (__nv_bfloat16 *) Vt);
     CKL();
-    lat_qcat_kernel<<<dim3((unsigned) nq, (unsigned) H), 128, 0, st>>>(q, H * (L.dim + L.rot_dim), qlat, H, L.dim, L.rot_dim, L.rot_dims, R, L.scale, b.pos, rope, t0, Qc);
+    pib_launch(lat_qcat_kernel, dim3(dim3((unsigned) nq, (unsigned) H)), dim3(128), (size_t) (0), st, q, H * (L.dim + L.rot_dim), qlat, H, L.dim, L.rot_dim, L.rot_dims, R, L.scale, b.pos, rope, t0, Qc);
     CKL();
     pib_mm a;
     a.W = Kb; a.wtype = PIB_TYPE_BF16; a.ldw = RK; a.X = Qc; a.ldx = RK; a.Y = S; a.ldy = NKp; a.M = nq * H; a.N = NK; a.K = RK;
     int rc = pib_dense_mm(a, st);
     if (rc != PIB_OK) return rc;
-    lat_softmax_kernel<<<nq * H, 256, 0, st>>>(S, NKp, NK, j0, L.window, b.pos, t0, H, L.sink);
+    pib_launch(lat_softmax_kernel, dim3(nq * H), dim3(256), (size_t) (0), st, S, NKp, NK, j0, L.window, b.pos, t0, H, L.sink);
     CKL();
     pib_mm v;
     v.W = Vt; v.wtype = PIB_TYPE_BF16; v.ldw = NKp; v.X = S; v.ldx = NKp; v.Y = ctx + (size_t) t0 * H * R; v.ldy = R; v.M = nq * H; v.N = R; v.K = NKp;
@@ -363,6 +383,8 @@ int pib_latent_attention_mm(const float * q, const float * qlat, const pib_hlaye
 // ---- HGRN2 ----------------------------------------------------------------------------------------------------------------------
 // in place on the projection rows [q | f | v]: q <- silu(q), f <- lower + (1 - lower) * sigmoid(f + bias)
 __global__ void hgrn2_gate_kernel(float * __restrict__ qfv, int ld, const float * __restrict__ f_bias, const float * __restrict__ lower, int T, int HD) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
     const int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (int64_t) T * HD) return;
     const int t = (int) (i / HD), c = (int) (i % HD);
@@ -374,7 +396,7 @@ __global__ void hgrn2_gate_kernel(float * __restrict__ qfv, int ld, const float 
 }
 int pib_hgrn2_gates(float * qfv, int ld, const float * f_bias, const float * lower, int T, int HD, cudaStream_t st) {
     const int64_t n = (int64_t) T * HD;
-    hgrn2_gate_kernel<<<(unsigned) ((n + 255) / 256), 256, 0, st>>>(qfv, ld, f_bias, lower, T, HD);
+    pib_launch(hgrn2_gate_kernel, dim3((unsigned) ((n + 255) / 256)), dim3(256), (size_t) (0), st, qfv, ld, f_bias, lower, T, HD);
     CKL();
     return PIB_OK;
 }
@@ -390,6 +412,8 @@ template <int RPT>
 __global__ void __launch_bounds__(16 * HG_VT) hgrn2_scan_kernel(const float * __restrict__ qfv, int ld, int H, int D, int V, const int32_t * __restrict__ seg_start,
                                                                 const int32_t * __restrict__ seg_len, const int32_t * __restrict__ seg_slot, float * __restrict__ state,
                                                                 size_t state_stride, size_t state_off, float * __restrict__ out) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
     extern __shared__ float hs[];                  // 2 x [HG_CHUNK][2 D + HG_VT]: the chunk being walked and the one in flight (cp.async)
     const int sg = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * HG_VT, part = threadIdx.x & 15, vl = threadIdx.x >> 4, vd = v0 + vl;
     const int s0 = seg_start[sg], n = seg_len[sg], HD = H * D, row_f = 2 * D + HG_VT, d0 = part * RPT;
@@ -445,6 +469,8 @@ __global__ void __launch_bounds__(16 * HG_VT) hgrn2_scan_kernel(const float * __
 
 // one warp per (token, head): o <- o / sqrt(mean(o^2) + eps) * w
 __global__ void head_rmsnorm_kernel(float * __restrict__ o, int n_rows, int V, const float * __restrict__ w, float eps) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
     const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (row >= n_rows) return;
     float * r = o + (size_t) row * V;
@@ -460,18 +486,20 @@ int pib_hgrn2_scan(const float * qfv, int ld, const pib_hlayer & L, const pib_hb
     if (D > 256) { pib_set_error("hgrn2: dim %d not supported (up to 256)", D); return PIB_ERR_UNSUPP; }
     dim3 grid((unsigned) b.S, (unsigned) H, (unsigned) ((V + HG_VT - 1) / HG_VT));
     const size_t smem = (size_t) 2 * HG_CHUNK * (2 * D + HG_VT) * 4;
-    if (D <= 64)       hgrn2_scan_kernel<4><<<grid, 16 * HG_VT, smem, st>>>(qfv, ld, H, D, V, b.seg_start, b.seg_len, b.seg_slot, state, state_stride, L.state_off, out);
-    else if (D <= 128) hgrn2_scan_kernel<8><<<grid, 16 * HG_VT, smem, st>>>(qfv, ld, H, D, V, b.seg_start, b.seg_len, b.seg_slot, state, state_stride, L.state_off, out);
-    else               hgrn2_scan_kernel<16><<<grid, 16 * HG_VT, smem, st>>>(qfv, ld, H, D, V, b.seg_start, b.seg_len, b.seg_slot, state, state_stride, L.state_off, out);
+    if (D <= 64)       pib_launch(hgrn2_scan_kernel<4>, dim3(grid), dim3(16 * HG_VT), (size_t) (smem), st, qfv, ld, H, D, V, b.seg_start, b.seg_len, b.seg_slot, state, state_stride, L.state_off, out);
+    else if (D <= 128) pib_launch(hgrn2_scan_kernel<8>, dim3(grid), dim3(16 * HG_VT), (size_t) (smem), st, qfv, ld, H, D, V, b.seg_start, b.seg_len, b.seg_slot, state, state_stride, L.state_off, out);
+    else               pib_launch(hgrn2_scan_kernel<16>, dim3(grid), dim3(16 * HG_VT), (size_t) (smem), st, qfv, ld, H, D, V, b.seg_start, b.seg_len, b.seg_slot, state, state_stride, L.state_off, out);
     CKL();
     const int n_rows = b.T * H;
-    head_rmsnorm_kernel<<<(n_rows + 7) / 8, 256, 0, st>>>(out, n_rows, V, onorm, eps);
+    pib_launch(head_rmsnorm_kernel, dim3((n_rows + 7) / 8), dim3(256), (size_t) (0), st, out, n_rows, V, onorm, eps);
     CKL();
     return PIB_OK;
 }
 
 // ---- PolyNorm: z <- a N(z) + b N(z^2) + c N(z^3) + e, N(u) = u / sqrt(mean(u^2) + eps) over the token's row ---------------------------
 __global__ void __launch_bounds__(256) polynorm_kernel(float * __restrict__ z, int F, float a, float b, float c, float e, float eps) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
     __shared__ float red[32];
     float * r = z + (size_t) blockIdx.x * F;
     float s2 = 0.f, s4 = 0.f, s6 = 0.f;
@@ -482,7 +510,7 @@ __global__ void __launch_bounds__(256) polynorm_kernel(float * __restrict__ z, i
     for (int i = threadIdx.x; i < F; i += blockDim.x) { const float v = r[i]; r[i] = fmaf(v, n1, fmaf(v * v, n2, fmaf(v * v * v, n3, e))); }
 }
 int pib_polynorm(float * z, int T, int F, const float * act4, float eps, cudaStream_t st) {
-    polynorm_kernel<<<T, 256, 0, st>>>(z, F, act4[0], act4[1], act4[2], act4[3], eps);
+    pib_launch(polynorm_kernel, dim3(T), dim3(256), (size_t) (0), st, z, F, act4[0], act4[1], act4[2], act4[3], eps);
     CKL();
     return PIB_OK;
 }
@@ -491,6 +519,8 @@ int pib_polynorm(float * z, int T, int F, const float * act4, float eps, cudaStr
 // one warp per token: softmax over the E router logits, the `top` largest scores (ties: the lower index), weights = score / (sum of the chosen + 1e-20)
 #define MOE_MAX_TOP 16
 __global__ void moe_route_kernel(const float * __restrict__ logits, int T, int E, int top, int32_t * __restrict__ ids, float * __restrict__ wts) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
     const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (t >= T) return;
     const float * z = logits + (size_t) t * E;
@@ -525,7 +555,7 @@ __global__ void moe_route_kernel(const float * __restrict__ logits, int T, int E
 }
 int pib_moe_route(const float * logits, int T, int E, int top, int32_t * ids, float * wts, cudaStream_t st) {
     if (top > MOE_MAX_TOP || top > E) { pib_set_error("router: top %d of %d experts (max %d)", top, E, MOE_MAX_TOP); return PIB_ERR_UNSUPP; }
-    moe_route_kernel<<<(T + 7) / 8, 256, 0, st>>>(logits, T, E, top, ids, wts);
+    pib_launch(moe_route_kernel, dim3((T + 7) / 8), dim3(256), (size_t) (0), st, logits, T, E, top, ids, wts);
     CKL();
     return PIB_OK;
 }
@@ -533,6 +563,8 @@ int pib_moe_route(const float * logits, int T, int E, int top, int32_t * ids, fl
 // pairs (token, k) grouped by expert, inside an expert in pair order: counts[e]; offs[e] = first sorted position of expert e;
 // perm[sorted position] = pair; inv[pair] = sorted position.  No atomics: the order, and so every sum formed from it, is fixed.
 __global__ void __launch_bounds__(256) moe_count_kernel(const int32_t * __restrict__ ids, int n_pairs, int32_t * __restrict__ counts) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
     __shared__ float red[32];
     const int e = blockIdx.x;
     int n = 0;
@@ -542,6 +574,8 @@ __global__ void __launch_bounds__(256) moe_count_kernel(const int32_t * __restri
 }
 __global__ void __launch_bounds__(256) moe_fill_kernel(const int32_t * __restrict__ ids, int n_pairs, int E, const int32_t * __restrict__ counts,
                                                        int32_t * __restrict__ offs, int32_t * __restrict__ perm, int32_t * __restrict__ inv) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
     __shared__ int wsum[8];
     __shared__ int base_s;
     const int e = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -573,9 +607,9 @@ __global__ void __launch_bounds__(256) moe_fill_kernel(const int32_t * __restric
 }
 int pib_moe_sort(const int32_t * ids, int n_pairs, int E, int32_t * counts, int32_t * offs, int32_t * perm, int32_t * inv, cudaStream_t st) {
     if (n_pairs >= (1 << 24)) { pib_set_error("router: %d pairs in one batch", n_pairs); return PIB_ERR_UNSUPP; }
-    moe_count_kernel<<<E, 256, 0, st>>>(ids, n_pairs, counts);
+    pib_launch(moe_count_kernel, dim3(E), dim3(256), (size_t) (0), st, ids, n_pairs, counts);
     CKL();
-    moe_fill_kernel<<<E, 256, 0, st>>>(ids, n_pairs, E, counts, offs, perm, inv);
+    pib_launch(moe_fill_kernel, dim3(E), dim3(256), (size_t) (0), st, ids, n_pairs, E, counts, offs, perm, inv);
     CKL();
     return PIB_OK;
 }
@@ -583,6 +617,8 @@ int pib_moe_sort(const int32_t * ids, int n_pairs, int E, int32_t * counts, int3
 // y[t] = shared[t] + sum_k w[t][k] * edn[inv[t * top + k]]   (k in ascending order)
 __global__ void moe_combine_kernel(const float * __restrict__ shared, const float * __restrict__ edn, const float * __restrict__ wts, const int32_t * __restrict__ inv,
                                    int top, int W, float * __restrict__ y) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
     const int t = blockIdx.x;
     for (int c = threadIdx.x; c < W; c += blockDim.x) {
         float acc = shared ? shared[(size_t) t * W + c] : 0.f;
@@ -591,7 +627,7 @@ __global__ void moe_combine_kernel(const float * __restrict__ shared, const floa
     }
 }
 int pib_moe_combine(const float * shared, const float * edn, const float * wts, const int32_t * inv, int T, int top, int W, float * y, cudaStream_t st) {
-    moe_combine_kernel<<<T, 256, 0, st>>>(shared, edn, wts, inv, top, W, y);
+    pib_launch(moe_combine_kernel, dim3(T), dim3(256), (size_t) (0), st, shared, edn, wts, inv, top, W, y);
     CKL();
     return PIB_OK;
 }
