@@ -312,3 +312,44 @@ def test_greedy_generation_through_the_scheduler(tmp_path, float32):
         if best != t:
             assert lg[best] - lg[t] < (1e-3 if float32 else 0.15) * spread(lg), "token %d instead of %d" % (t, best)
         lg = O.forward(cfg, W, seq, [t])[-1]
+
+
+def test_trace_runner_replays_steps(tmp_path):
+    """bin/trace_run as a user starts it: JSON steps on standard input (portions beside single tokens, requests ending, more requests
+    than state slots over time, cells for the live ones only), logits files out, one 'done' line per step"""
+    import json
+    import os
+    import subprocess
+    import sys
+    cfg = CONFIGS["mixed_small"]()
+    W = O.random_weights(cfg, 24)
+    model = tmp_path / "model"
+    O.write_model(str(model), cfg, W)
+    reqs = {"a": tokens(cfg, 50, 1), "b": tokens(cfg, 21, 2), "c": tokens(cfg, 33, 3), "d": tokens(cfg, 2, 4), "e": tokens(cfg, 40, 5)}
+    refs = {k: oracle_logits(cfg, W, v) for k, v in reqs.items()}
+    plan = [[("a", 30), ("b", 2)], [("a", 1), ("b", 19), ("c", 7)], [("a", 19), ("c", 1)], [("c", 25), ("d", 2)], [("e", 38)], [("e", 1)], [("e", 1)]]
+    at, steps, wanted = {k: 0 for k in reqs}, [], []
+    for n, step in enumerate(plan):
+        entries, end, rows = [], [], []
+        for rid, cnt in step:
+            lo, hi = at[rid], at[rid] + cnt
+            want = sorted({0, cnt - 1}) if cnt > 1 else [0]
+            entries.append({"id": rid, "tokens": reqs[rid][lo:hi], "want": want})
+            rows += [(rid, lo + w) for w in want]
+            at[rid] = hi
+            if hi == len(reqs[rid]):
+                end.append(rid)
+        steps.append(json.dumps({"step": n, "entries": entries, "end": end}))
+        wanted.append(rows)
+    steps.insert(3, json.dumps({"step": 99, "entries": [], "end": []}))          # a step that brings nothing still answers
+    root = os.path.abspath(os.path.join(os.path.dirname(__file__), ".."))
+    for dtype, tol in (("float32", TOL32), ("bfloat16", TOL16)):
+        out = tmp_path / ("out_" + dtype)
+        p = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", str(model), "--dtype", dtype, "--out", str(out),
+                            "--max-tokens", "128", "--slots", "3"], input="\n".join(steps) + "\n", capture_output=True, text=True, timeout=300)
+        assert p.returncode == 0, p.stderr[-2000:]
+        assert [l for l in p.stdout.split("\n") if l.startswith("done")] == ["done %d" % json.loads(s)["step"] for s in steps]
+        for n, rows in enumerate(wanted):
+            got = np.fromfile(out / ("%d.f32" % n), "<f4").reshape(len(rows), -1)
+            ref = np.stack([refs[rid][i] for rid, i in rows])
+            assert row_err(got, ref).max() < tol, (dtype, n)
