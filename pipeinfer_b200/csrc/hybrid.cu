@@ -123,8 +123,8 @@ static int grow_attn_mm(pib_context * c, const pib_hlayer & L, int nq, int NK) {
         if (cudaMalloc(p, *cap) != cudaSuccess) { cudaGetLastError(); *p = nullptr; *cap = 0; return false; }
         return true;
     };
-    if (!grow(&x->am_kb, &x->am_kb_cap, NKp * RK * 2) || !grow(&x->am_vt, &x->am_vt_cap, R * NKp * 2) || !grow((void **) &x->am_q, &x->am_q_cap, rows * RK * 4) ||
-        !grow((void **) &x->am_s, &x->am_s_cap, rows * NKp * 4)) { pib_set_error("decode: out of memory for the attention's score rows"); return PIB_ERR_NOMEM; }
+    if (!grow(&x->am_kb, &x->am_kb_cap, NKp * RK * 2) || !grow(&x->am_vt, &x->am_vt_cap, R * NKp * 4) || !grow((void **) &x->am_q, &x->am_q_cap, rows * RK * 4) ||
+        !grow((void **) &x->am_s, &x->am_s_cap, rows * NKp * 8)) { pib_set_error("decode: out of memory for the attention's score rows"); return PIB_ERR_NOMEM; }
     return PIB_OK;
 }
 

@@ -296,7 +296,8 @@ int pib_latent_attention(const float * q, const float * qlat, const pib_hlayer &
 // ---- latent attention as matmuls (long portions, served mode) ----------------------------------------------------------------------
 // For a block of consecutive tokens of one segment the scores against the block's key range [j0, j0 + NK) are one matmul, the masked
 // softmax with the sink one pass over the score rows, and the weighted sums of latent rows a second matmul.  These kernels prepare the
-// operands: the keys' rows as bfloat16 [NK][R + rot_dim] and, transposed, [R][NKp] (NKp = NK rounded up to 8, the pad zero), and the
+// operands: the keys' rows as bfloat16 [NK][R + rot_dim] and, transposed and twice side by side, [R][2 NKp] (NKp = NK rounded up to 8, the pad zero;
+// twice because a weight enters the value matmul as its bfloat16 part plus the remainder of that rounding), and the
 // queries as rows [(token, head)][R + rot_dim] = scale * [W_uk^T q | rotated q part].
 __global__ void __launch_bounds__(128) lat_gather_kernel(const float * __restrict__ cache, int cache_row, const int32_t * __restrict__ map, int j0, int NK, int NKp, int R,
                                                          int RK, __nv_bfloat16 * __restrict__ Kb, __nv_bfloat16 * __restrict__ Vt) {
@@ -308,10 +309,10 @@ __global__ void __launch_bounds__(128) lat_gather_kernel(const float * __restric
         for (int i = threadIdx.x; i < RK; i += blockDim.x) {
             const __nv_bfloat16 v = __float2bfloat16_rn(row[i]);
             Kb[(size_t) j * RK + i] = v;
-            if (i < R) Vt[(size_t) i * NKp + j] = v;
+            if (i < R) { Vt[(size_t) i * 2 * NKp + j] = v; Vt[(size_t) i * 2 * NKp + NKp + j] = v; }
         }
     } else {
-        for (int i = threadIdx.x; i < R; i += blockDim.x) Vt[(size_t) i * NKp + j] = __float2bfloat16_rn(0.f);
+        for (int i = threadIdx.x; i < R; i += blockDim.x) { Vt[(size_t) i * 2 * NKp + j] = __float2bfloat16_rn(0.f); Vt[(size_t) i * 2 * NKp + NKp + j] = __float2bfloat16_rn(0.f); }
     }
 }
 __global__ void __launch_bounds__(128) lat_qcat_kernel(const float * __restrict__ q, int ldq, const float * __restrict__ qlat, int H, int D, int rot_dim, int rot_dims, int R,
@@ -340,7 +341,7 @@ __global__ void __launch_bounds__(256) lat_softmax_kernel(float * __restrict__ S
     pib_pdl_trigger();
     __shared__ float red[32];
     const int row = blockIdx.x, t = t0 + row / H, h = row % H, p = pos[t];
-    float *   s = S + (size_t) row * NKp;
+    float *   s = S + (size_t) row * 2 * NKp;      // [weights' bfloat16 part | what the rounding left]: the value matmul sees both, so the weights keep fp32 accuracy
     const int lo = max(0, p - window + 1) - j0, hi = p - j0;            // valid columns [lo, hi]
     const float sk = sink[h];
     float m = sk;
@@ -357,8 +358,12 @@ __global__ void __launch_bounds__(256) lat_softmax_kernel(float * __restrict__ S
         sum += e;
     }
     const float inv = 1.0f / (block_sum(sum, red) + expf(sk - m));
-    for (int j = lo + (int) threadIdx.x; j <= hi; j += blockDim.x) s[j] *= inv;
-    (void) NK;
+    for (int j = threadIdx.x; j < NKp; j += blockDim.x) {
+        const float p = s[j] * inv, hi16 = __bfloat162float(__float2bfloat16_rn(p));
+        s[j] = hi16;
+        s[NKp + j] = p - hi16;
+    }
+    (void) NK; (void) hi;
 }
 
 // the block of `nq` tokens starting at batch row t0 (positions p0 ..), keys [j0, j0 + NK): ctx rows [(token, head)][R] of those tokens
@@ -370,13 +375,13 @@ int pib_latent_attention_mm(const float * q, const float * qlat, const pib_hlaye
     pib_launch(lat_qcat_kernel, dim3(dim3((unsigned) nq, (unsigned) H)), dim3(128), (size_t) (0), st, q, H * (L.dim + L.rot_dim), qlat, H, L.dim, L.rot_dim, L.rot_dims, R, L.scale, b.pos, rope, t0, Qc);
     CKL();
     pib_mm a;
-    a.W = Kb; a.wtype = PIB_TYPE_BF16; a.ldw = RK; a.X = Qc; a.ldx = RK; a.Y = S; a.ldy = NKp; a.M = nq * H; a.N = NK; a.K = RK;
+    a.W = Kb; a.wtype = PIB_TYPE_BF16; a.ldw = RK; a.X = Qc; a.ldx = RK; a.Y = S; a.ldy = 2 * NKp; a.M = nq * H; a.N = NK; a.K = RK;
     int rc = pib_dense_mm(a, st);
     if (rc != PIB_OK) return rc;
     pib_launch(lat_softmax_kernel, dim3(nq * H), dim3(256), (size_t) (0), st, S, NKp, NK, j0, L.window, b.pos, t0, H, L.sink);
     CKL();
     pib_mm v;
-    v.W = Vt; v.wtype = PIB_TYPE_BF16; v.ldw = NKp; v.X = S; v.ldx = NKp; v.Y = ctx + (size_t) t0 * H * R; v.ldy = R; v.M = nq * H; v.N = R; v.K = NKp;
+    v.W = Vt; v.wtype = PIB_TYPE_BF16; v.ldw = 2 * NKp; v.X = S; v.ldx = 2 * NKp; v.Y = ctx + (size_t) t0 * H * R; v.ldy = R; v.M = nq * H; v.N = R; v.K = 2 * NKp;
     return pib_dense_mm(v, st);
 }
 
