@@ -407,69 +407,72 @@ int pib_hgrn2_gates(float * qfv, int ld, const float * f_bias, const float * low
 }
 
 // grid (segment, head, tile of HG_VT value columns), 16 * HG_VT threads: the 16 lanes of a half-warp share one column of the head's
-// matrix, lane `part` keeping rows part * RPT .. + RPT - 1 in registers (columns are independent, so a head is spread over vdim / HG_VT
-// CTAs and the machine holds several warps per scheduler).  A step is s <- v + f (s - v) (= f s + (1 - f) v) and a dot product with q,
-// reduced over the 16 lanes by shuffles.  The tokens' q, f and v come through shared memory in chunks of HG_CHUNK tokens; the matrix
-// is read from the slot at the start of the segment and left there at its end.
+// matrix, lane `part` keeping rows part, part + 16, part + 32, ... in registers (columns are independent, so a head is spread over
+// vdim / HG_VT CTAs and the machine holds several warps per scheduler; neighbouring lanes read neighbouring words of shared memory, no
+// bank conflicts).  A step is s <- v + f (s - v) (= f s + (1 - f) v) and a dot product with q, reduced over the 16 lanes by shuffles.
+// The tokens' q, f and v come through shared memory in chunks of HG_CHUNK tokens, the next chunk in flight (cp.async) while this one is
+// walked; the matrix is read from the slot at the start of the segment and left there at its end.  FULL: dim == 16 RPT, no row guards.
 #define HG_CHUNK 16
 #define HG_VT    8
-template <int RPT>
+template <int RPT, bool FULL>
 __global__ void __launch_bounds__(16 * HG_VT) hgrn2_scan_kernel(const float * __restrict__ qfv, int ld, int H, int D, int V, const int32_t * __restrict__ seg_start,
                                                                 const int32_t * __restrict__ seg_len, const int32_t * __restrict__ seg_slot, float * __restrict__ state,
                                                                 size_t state_stride, size_t state_off, float * __restrict__ out) {
     pib_pdl_wait();
     pib_pdl_trigger();
-    extern __shared__ float hs[];                  // 2 x [HG_CHUNK][2 D + HG_VT]: the chunk being walked and the one in flight (cp.async)
+    extern __shared__ float hs[];                  // 2 x [HG_CHUNK][2 D + HG_VT]: the chunk being walked and the one in flight
     const int sg = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * HG_VT, part = threadIdx.x & 15, vl = threadIdx.x >> 4, vd = v0 + vl;
-    const int s0 = seg_start[sg], n = seg_len[sg], HD = H * D, row_f = 2 * D + HG_VT, d0 = part * RPT;
+    const int s0 = seg_start[sg], n = seg_len[sg], HD = H * D, row_f = 2 * D + HG_VT;
     const bool vok = vd < V;
     float *   S = state + (size_t) seg_slot[sg] * state_stride + state_off + (size_t) h * D * V;
     float s[RPT];
 #pragma unroll
-    for (int r = 0; r < RPT; r++) s[r] = (d0 + r < D && vok) ? S[(size_t) (d0 + r) * V + vd] : 0.f;
+    for (int r = 0; r < RPT; r++) { const int d = part + 16 * r; s[r] = ((FULL || d < D) && vok) ? S[(size_t) d * V + vd] : 0.f; }
     auto fetch = [&](int c0, int buf) {
         const int nc = min(HG_CHUNK, n - c0);
         for (int t = 0; t < nc; t++) {
-            const float * row = qfv + (size_t) (s0 + c0 + t) * ld;
-            const uint32_t dst = (uint32_t) __cvta_generic_to_shared(hs + (size_t) (buf * HG_CHUNK + t) * row_f);
+            const float * row = qfv + (size_t) (s0 + c0 + t) * ld + (size_t) h * D;
+            const uint32_t dst = (uint32_t) __cvta_generic_to_shared(hs + (buf * HG_CHUNK + t) * row_f);
             for (int e = threadIdx.x; e < D; e += blockDim.x) {
-                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + 4u * e), "l"(row + (size_t) h * D + e) : "memory");
-                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + 4u * (D + e)), "l"(row + HD + (size_t) h * D + e) : "memory");
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + 4u * e), "l"(row + e) : "memory");
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + 4u * (D + e)), "l"(row + HD + e) : "memory");
             }
             if (threadIdx.x < HG_VT && v0 + (int) threadIdx.x < V)
-                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + 4u * (2 * D + threadIdx.x)), "l"(row + 2 * HD + (size_t) h * V + v0 + threadIdx.x) : "memory");
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + 4u * (2 * D + threadIdx.x)), "l"(qfv + (size_t) (s0 + c0 + t) * ld + 2 * HD + (size_t) h * V + v0 + threadIdx.x) : "memory");
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
     if (n > 0) fetch(0, 0);
     int buf = 0;
+    float * op = out + (size_t) s0 * H * V + (size_t) h * V + vd;
+    const int ostride = H * V;
     for (int c0 = 0; c0 < n; c0 += HG_CHUNK, buf ^= 1) {
         const int nc = min(HG_CHUNK, n - c0);
         if (c0 + HG_CHUNK < n) { fetch(c0 + HG_CHUNK, buf ^ 1); asm volatile("cp.async.wait_group 1;" ::: "memory"); }
         else                   asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();
+        const float * qp = hs + buf * HG_CHUNK * row_f + part;
 #pragma unroll 4
-        for (int t = 0; t < nc; t++) {
-            const float * qp = hs + (size_t) (buf * HG_CHUNK + t) * row_f, * fp = qp + D;
-            const float   v = vok ? qp[2 * D + vl] : 0.f;
+        for (int t = 0; t < nc; t++, qp += row_f, op += ostride) {
+            const float v = vok ? qp[2 * D + vl - part] : 0.f;
             float acc = 0.f;
 #pragma unroll
             for (int r = 0; r < RPT; r++) {
-                if (d0 + r < D) {
-                    s[r] = fmaf(fp[d0 + r], s[r] - v, v);
-                    acc = fmaf(qp[d0 + r], s[r], acc);
+                if (FULL || part + 16 * r < D) {
+                    s[r] = fmaf(qp[D + 16 * r], s[r] - v, v);
+                    acc = fmaf(qp[16 * r], s[r], acc);
                 }
             }
             acc += __shfl_xor_sync(0xffffffffu, acc, 1);
             acc += __shfl_xor_sync(0xffffffffu, acc, 2);
             acc += __shfl_xor_sync(0xffffffffu, acc, 4);
             acc += __shfl_xor_sync(0xffffffffu, acc, 8);
-            if (part == 0 && vok) out[(size_t) (s0 + c0 + t) * H * V + (size_t) h * V + vd] = acc;
+            if (part == 0 && vok) *op = acc;
         }
         __syncthreads();                           // everyone is done with this buffer before the fetch after next refills it
     }
 #pragma unroll
-    for (int r = 0; r < RPT; r++) if (d0 + r < D && vok) S[(size_t) (d0 + r) * V + vd] = s[r];
+    for (int r = 0; r < RPT; r++) { const int d = part + 16 * r; if ((FULL || d < D) && vok) S[(size_t) d * V + vd] = s[r]; }
 }
 
 // one warp per (token, head): o <- o / sqrt(mean(o^2) + eps) * w
@@ -491,9 +494,14 @@ int pib_hgrn2_scan(const float * qfv, int ld, const pib_hlayer & L, const pib_hb
     if (D > 256) { pib_set_error("hgrn2: dim %d not supported (up to 256)", D); return PIB_ERR_UNSUPP; }
     dim3 grid((unsigned) b.S, (unsigned) H, (unsigned) ((V + HG_VT - 1) / HG_VT));
     const size_t smem = (size_t) 2 * HG_CHUNK * (2 * D + HG_VT) * 4;
-    if (D <= 64)       pib_launch(hgrn2_scan_kernel<4>, dim3(grid), dim3(16 * HG_VT), (size_t) (smem), st, qfv, ld, H, D, V, b.seg_start, b.seg_len, b.seg_slot, state, state_stride, L.state_off, out);
-    else if (D <= 128) pib_launch(hgrn2_scan_kernel<8>, dim3(grid), dim3(16 * HG_VT), (size_t) (smem), st, qfv, ld, H, D, V, b.seg_start, b.seg_len, b.seg_slot, state, state_stride, L.state_off, out);
-    else               pib_launch(hgrn2_scan_kernel<16>, dim3(grid), dim3(16 * HG_VT), (size_t) (smem), st, qfv, ld, H, D, V, b.seg_start, b.seg_len, b.seg_slot, state, state_stride, L.state_off, out);
+#define HG_GO(RPT, FULL) pib_launch(hgrn2_scan_kernel<RPT, FULL>, dim3(grid), dim3(16 * HG_VT), (size_t) (smem), st, qfv, ld, H, D, V, b.seg_start, b.seg_len, b.seg_slot, state, \
+                                    state_stride, L.state_off, out)
+    if (D == 64)       HG_GO(4, true);
+    else if (D == 128) HG_GO(8, true);
+    else if (D <= 64)  HG_GO(4, false);
+    else if (D <= 128) HG_GO(8, false);
+    else               HG_GO(16, false);
+#undef HG_GO
     CKL();
     const int n_rows = b.T * H;
     pib_launch(head_rmsnorm_kernel, dim3((n_rows + 7) / 8), dim3(256), (size_t) (0), st, out, n_rows, V, onorm, eps);
