@@ -213,6 +213,7 @@ int pib_dense_mm(const pib_mm & a, cudaStream_t st) {
         const int rc = pib_dense_mm_tc(a, st);
         if (rc != PIB_ERR_UNSUPP) return rc;
     }
+    if (a.x_bf16) { pib_set_error("dense matmul: bfloat16 activations need the tensor-core path (more than 16 rows, strides multiples of 8)"); return PIB_ERR_UNSUPP; }
     mm_dev d = { a.W, a.ldw, a.wz, a.X, a.ldx, a.xz, a.xrows, a.xdiv < 1 ? 1 : a.xdiv, a.Y, a.ldy, a.yz, a.M, a.N, a.K, a.zrange };
 #define MM_GO(WT, ROUND) (a.epi == PIB_EPI_RELU2 ? launch_mm<WT, ROUND, PIB_EPI_RELU2>(a, d, st) : launch_mm<WT, ROUND, PIB_EPI_NONE>(a, d, st))
     if (a.wtype == PIB_TYPE_BF16) return MM_GO(__nv_bfloat16, true);

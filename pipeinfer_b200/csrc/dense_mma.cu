@@ -6,7 +6,8 @@
 //   warp 1       allocates tensor memory; one lane issues tcgen05.mma.cta_group::1.kind::f16 (bf16 x bf16 -> fp32, M 128, N NB, 4 x K 16 per
 //                k-step) and commits each stage back to the producer, the last one to the epilogue
 //   warps 2..5   read the accumulators (tcgen05.ld.32x32b: a lane is a weight row, a column a token) and store Y, optionally relu^2
-// The activations are fp32 in the layer buffers; dense_cast_kernel writes them once as bfloat16 rows (gathered through the row list
+// The activations are fp32 in the layer buffers (a producer that can write bfloat16 rows itself passes them as they are: x_bf16);
+// otherwise dense_cast_kernel writes them once as bfloat16 rows (gathered through the row list
 // of a grouped problem, so that every expert's tokens are neighbours) -- the TMA source.  Tails in K, N and M are zero-filled by TMA
 // and masked at the store.  Tensor maps are 3-D {k, row, z}: heads of an attention layer and experts of a mixture are the z axis.
 // Every mbarrier wait is bounded: a wait that runs out raises the CTA's abort flag and an error word that the host reads.
@@ -268,16 +269,18 @@ int pib_dense_mm_tc(const pib_mm & a, cudaStream_t st) {
     const int  Kp = (a.K + 7) & ~7;
     const bool grouped = a.zrange != nullptr;
     const int  Zs = grouped ? 1 : a.Z;
-    dt_scratch * sc = dt_scratch_of(st, (size_t) Zs * a.M * Kp * 2 + 256);
-    if (!sc || !sc->xs) return PIB_ERR_UNSUPP;
-    pib_launch(dense_cast_kernel, dim3(dim3((unsigned) a.M, (unsigned) Zs)), dim3(128), (size_t) (0), st, a.X, a.ldx, a.xz, a.xrows, a.xdiv < 1 ? 1 : a.xdiv, a.M, a.K, Kp, sc->xs);
+    if (a.x_bf16 && (grouped || a.xrows || a.Z != 1 || a.ldx % 8 || ((uintptr_t) a.X & 15))) return PIB_ERR_UNSUPP;
+    dt_scratch * sc = dt_scratch_of(st, a.x_bf16 ? 0 : (size_t) Zs * a.M * Kp * 2 + 256);
+    if (!sc || (!a.x_bf16 && !sc->xs)) return PIB_ERR_UNSUPP;
+    if (!a.x_bf16) pib_launch(dense_cast_kernel, dim3(dim3((unsigned) a.M, (unsigned) Zs)), dim3(128), (size_t) (0), st, a.X, a.ldx, a.xz, a.xrows, a.xdiv < 1 ? 1 : a.xdiv, a.M, a.K, Kp, sc->xs);
     PIB_CHECK(cudaGetLastError());
     // the token tile: as wide as the rows of one problem allow (grouped problems: the average share of an expert)
     const int per = grouped ? (a.M + a.Z - 1) / a.Z : a.M;
     const int NB = per <= 32 ? 32 : per <= 64 ? 64 : 128;
     CUtensorMap wmap, xmap;
     int rc = dt_map3(&wmap, a.W, (uint64_t) a.K, (uint64_t) a.N, (uint64_t) a.Z, (uint64_t) a.ldw * 2, (uint64_t) (a.Z > 1 ? a.wz : (int64_t) a.N * a.ldw) * 2, DT_BM);
-    if (rc == PIB_OK) rc = dt_map3(&xmap, sc->xs, (uint64_t) Kp, (uint64_t) a.M, (uint64_t) Zs, (uint64_t) Kp * 2, (uint64_t) a.M * Kp * 2, (uint32_t) NB);
+    if (rc == PIB_OK && a.x_bf16) rc = dt_map3(&xmap, a.X, (uint64_t) a.K, (uint64_t) a.M, 1, (uint64_t) a.ldx * 2, (uint64_t) a.M * a.ldx * 2, (uint32_t) NB);
+    else if (rc == PIB_OK) rc = dt_map3(&xmap, sc->xs, (uint64_t) Kp, (uint64_t) a.M, (uint64_t) Zs, (uint64_t) Kp * 2, (uint64_t) a.M * Kp * 2, (uint32_t) NB);
     if (rc != PIB_OK) return rc;
     switch (NB) {
         case 32:  return dt_launch<32>(a, wmap, xmap, grouped ? 0 : 1, sc->err, st);

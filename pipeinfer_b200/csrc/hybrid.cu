@@ -35,8 +35,8 @@ struct pib_hybrid_ctx {
     int32_t *   meta_dev = nullptr;
     int         meta_cap = 0, meta_next = 0;
     // operands of the matmul form of the attention: keys [NK][row] and transposed latents [R][NKp] (bfloat16), query rows, score rows
-    void * am_kb = nullptr, * am_vt = nullptr; float * am_q = nullptr, * am_s = nullptr;
-    size_t am_kb_cap = 0, am_vt_cap = 0, am_q_cap = 0, am_s_cap = 0;
+    void * am_kb = nullptr, * am_vt = nullptr, * am_p = nullptr; float * am_q = nullptr, * am_s = nullptr;
+    size_t am_kb_cap = 0, am_vt_cap = 0, am_q_cap = 0, am_s_cap = 0, am_p_cap = 0;
     std::string kv_error;                       // set when a cache op arrived that the states cannot follow
     // per-launch timing (llama_pib_profile_layer(ctx, >= 0) switches it on): CUDA events around every launch of every layer
     struct Rec { int kind; double flops, bytes; cudaEvent_t e0, e1; };
@@ -124,7 +124,7 @@ static int grow_attn_mm(pib_context * c, const pib_hlayer & L, int nq, int NK) {
         return true;
     };
     if (!grow(&x->am_kb, &x->am_kb_cap, NKp * RK * 2) || !grow(&x->am_vt, &x->am_vt_cap, R * NKp * 4) || !grow((void **) &x->am_q, &x->am_q_cap, rows * RK * 4) ||
-        !grow((void **) &x->am_s, &x->am_s_cap, rows * NKp * 8)) { pib_set_error("decode: out of memory for the attention's score rows"); return PIB_ERR_NOMEM; }
+        !grow((void **) &x->am_s, &x->am_s_cap, rows * NKp * 8) || !grow(&x->am_p, &x->am_p_cap, rows * NKp * 4)) { pib_set_error("decode: out of memory for the attention's score rows"); return PIB_ERR_NOMEM; }
     return PIB_OK;
 }
 
@@ -143,7 +143,7 @@ void pib_hybrid_ctx_free(pib_context * c) {
     free_scratch(x);
     if (x->state) cudaFree(x->state);
     if (x->cellmap) cudaFree(x->cellmap);
-    for (void * p : { x->am_kb, x->am_vt, (void *) x->am_q, (void *) x->am_s }) if (p) cudaFree(p);
+    for (void * p : { x->am_kb, x->am_vt, x->am_p, (void *) x->am_q, (void *) x->am_s }) if (p) cudaFree(p);
     for (float * p : x->cache) if (p) cudaFree(p);
     for (float2 * p : x->rope) if (p) cudaFree(p);
     for (int i = 0; i < pib_hybrid_ctx::RING; i++) { if (x->meta_host[i]) cudaFreeHost(x->meta_host[i]); if (x->meta_ev[i]) cudaEventDestroy(x->meta_ev[i]); }
@@ -184,7 +184,7 @@ static int grow_scratch(pib_context * c, int T) {
 // MM_ATTN_MIN_ROW floats, a multiple of 8), in blocks of MM_ATTN_BLOCK tokens; everything else stays with latent_attn_kernel.
 #define MM_ATTN_MIN_LEN 128
 #define MM_ATTN_MIN_ROW 192
-#define MM_ATTN_BLOCK   256
+#define MM_ATTN_BLOCK   512
 struct pib_hseg { int start, len, seq, slot; bool fresh; };
 
 static int grow_attn_mm(pib_context * c, const pib_hlayer & L, int nq, int NK);
@@ -252,7 +252,7 @@ static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B, cons
                     if ((rc = grow_attn_mm(c, L, nq, NK)) != PIB_OK) return rc;
                     RC(HK_LATTN_MM, 2.0 * nq * H * (double) NK * (2.0 * R + rd), 2.0 * NK * (2.0 * R + rd) + 8.0 * nq * H * (2.0 * R + rd) + 8.0 * nq * H * (double) NK,
                        pib_latent_attention_mm(x->q, x->qlat, L, B, x->rope[L.rope_id], cache, row, x->cellmap + (size_t) g.slot * c->n_ctx, g.start + o, nq, j0, NK,
-                                               x->am_kb, x->am_vt, x->am_q, x->am_s, x->lat, st));
+                                               x->am_kb, x->am_vt, x->am_q, x->am_s, x->am_p, x->lat, st));
                     nk += 5;
                 }
             }

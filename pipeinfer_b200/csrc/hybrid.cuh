@@ -86,6 +86,7 @@ struct pib_mm {
     const int32_t * zrange = nullptr;                    // device [Z + 1]: z owns rows [zrange[z], zrange[z + 1]); null: all M rows, every z
     int             epi = PIB_EPI_NONE;
     int             exact = 0;                           // 1: operands stay fp32 (no bfloat16 rounding of X); W must be float32
+    int             x_bf16 = 0;                          // 1: X already holds bfloat16 rows (ldx in elements, a multiple of 8): tensor-core path only, no staging copy
 };
 int pib_dense_mm(const pib_mm & a, cudaStream_t st);
 int pib_dense_mm_check(cudaStream_t st, int enqueue);   // dense_mma.cu: the error word of the bounded waits (1: copy it in stream order, 0: read the copy)
@@ -107,7 +108,7 @@ int pib_latent_prep(const float * proj, int ldp, const pib_hlayer & L, const flo
 int pib_latent_attention(const float * q, const float * qlat, const pib_hlayer & L, const pib_hbatch & b, const float2 * rope, int rope_n_pos,
                          const float * cache, int cache_row, const int32_t * cellmap, int n_ctx, float * ctx, const int32_t * skip, cudaStream_t st);
 int pib_latent_attention_mm(const float * q, const float * qlat, const pib_hlayer & L, const pib_hbatch & b, const float2 * rope, const float * cache, int cache_row,
-                            const int32_t * map, int t0, int nq, int j0, int NK, void * Kb, void * Vt, float * Qc, float * S, float * ctx, cudaStream_t st);
+                            const int32_t * map, int t0, int nq, int j0, int NK, void * Kb, void * Vt, float * Qc, float * S, void * P, float * ctx, cudaStream_t st);
 int pib_hgrn2_gates(float * qfv, int ld, const float * f_bias, const float * lower, int T, int HD, cudaStream_t st);
 int pib_hgrn2_scan(const float * qfv, int ld, const pib_hlayer & L, const pib_hbatch & b, float * state, size_t state_stride, const float * onorm, float eps,
                    float * out, cudaStream_t st);

@@ -335,13 +335,14 @@ __global__ void __launch_bounds__(128) lat_qcat_kernel(const float * __restrict_
     }
 }
 // one score row per (token, head), in place: keys outside [p - window + 1, p] and the pad get weight 0, the sink one share of the denominator
-__global__ void __launch_bounds__(256) lat_softmax_kernel(float * __restrict__ S, int NKp, int NK, int j0, int window, const int32_t * __restrict__ pos, int t0, int H,
-                                                          const float * __restrict__ sink) {
+__global__ void __launch_bounds__(256) lat_softmax_kernel(float * __restrict__ S, __nv_bfloat16 * __restrict__ P, int NKp, int NK, int j0, int window,
+                                                          const int32_t * __restrict__ pos, int t0, int H, const float * __restrict__ sink) {
     pib_pdl_wait();
     pib_pdl_trigger();
     __shared__ float red[32];
     const int row = blockIdx.x, t = t0 + row / H, h = row % H, p = pos[t];
-    float *   s = S + (size_t) row * 2 * NKp;      // [weights' bfloat16 part | what the rounding left]: the value matmul sees both, so the weights keep fp32 accuracy
+    float *   s = S + (size_t) row * NKp;
+    __nv_bfloat16 * pw = P + (size_t) row * 2 * NKp;   // [weights' bfloat16 part | what the rounding left]: the value matmul sees both, so the weights keep fp32 accuracy
     const int lo = max(0, p - window + 1) - j0, hi = p - j0;            // valid columns [lo, hi]
     const float sk = sink[h];
     float m = sk;
@@ -359,29 +360,44 @@ __global__ void __launch_bounds__(256) lat_softmax_kernel(float * __restrict__ S
     }
     const float inv = 1.0f / (block_sum(sum, red) + expf(sk - m));
     for (int j = threadIdx.x; j < NKp; j += blockDim.x) {
-        const float p = s[j] * inv, hi16 = __bfloat162float(__float2bfloat16_rn(p));
-        s[j] = hi16;
-        s[NKp + j] = p - hi16;
+        const float p = s[j] * inv;
+        const __nv_bfloat16 hi16 = __float2bfloat16_rn(p);
+        pw[j] = hi16;
+        pw[NKp + j] = __float2bfloat16_rn(p - __bfloat162float(hi16));
     }
     (void) NK; (void) hi;
 }
 
+// bfloat16 weight rows back to fp32 rows (same pitch), for the few-row matmul kernels
+__global__ void lat_widen_kernel(const __nv_bfloat16 * __restrict__ P, int n, float * __restrict__ S) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
+    const __nv_bfloat16 * p = P + (size_t) blockIdx.x * n;
+    float * s = S + (size_t) blockIdx.x * n;
+    for (int j = threadIdx.x; j < n; j += blockDim.x) s[j] = __bfloat162float(p[j]);
+}
+
 // the block of `nq` tokens starting at batch row t0 (positions p0 ..), keys [j0, j0 + NK): ctx rows [(token, head)][R] of those tokens
 int pib_latent_attention_mm(const float * q, const float * qlat, const pib_hlayer & L, const pib_hbatch & b, const float2 * rope, const float * cache, int cache_row,
-                            const int32_t * map, int t0, int nq, int j0, int NK, void * Kb, void * Vt, float * Qc, float * S, float * ctx, cudaStream_t st) {
+                            const int32_t * map, int t0, int nq, int j0, int NK, void * Kb, void * Vt, float * Qc, float * S, void * P, float * ctx, cudaStream_t st) {
     const int H = L.heads, R = L.kv_rank, RK = R + L.rot_dim, NKp = (NK + 7) & ~7;
     pib_launch(lat_gather_kernel, dim3(NKp), dim3(128), (size_t) (0), st, cache, cache_row, map, j0, NK, NKp, R, RK, (__nv_bfloat16 *) Kb, (__nv_bfloat16 *) Vt);
     CKL();
     pib_launch(lat_qcat_kernel, dim3(dim3((unsigned) nq, (unsigned) H)), dim3(128), (size_t) (0), st, q, H * (L.dim + L.rot_dim), qlat, H, L.dim, L.rot_dim, L.rot_dims, R, L.scale, b.pos, rope, t0, Qc);
     CKL();
     pib_mm a;
-    a.W = Kb; a.wtype = PIB_TYPE_BF16; a.ldw = RK; a.X = Qc; a.ldx = RK; a.Y = S; a.ldy = 2 * NKp; a.M = nq * H; a.N = NK; a.K = RK;
+    a.W = Kb; a.wtype = PIB_TYPE_BF16; a.ldw = RK; a.X = Qc; a.ldx = RK; a.Y = S; a.ldy = NKp; a.M = nq * H; a.N = NK; a.K = RK;
     int rc = pib_dense_mm(a, st);
     if (rc != PIB_OK) return rc;
-    pib_launch(lat_softmax_kernel, dim3(nq * H), dim3(256), (size_t) (0), st, S, NKp, NK, j0, L.window, b.pos, t0, H, L.sink);
+    pib_launch(lat_softmax_kernel, dim3(nq * H), dim3(256), (size_t) (0), st, S, (__nv_bfloat16 *) P, NKp, NK, j0, L.window, b.pos, t0, H, L.sink);
     CKL();
     pib_mm v;
-    v.W = Vt; v.wtype = PIB_TYPE_BF16; v.ldw = 2 * NKp; v.X = S; v.ldx = 2 * NKp; v.Y = ctx + (size_t) t0 * H * R; v.ldy = R; v.M = nq * H; v.N = R; v.K = 2 * NKp;
+    v.W = Vt; v.wtype = PIB_TYPE_BF16; v.ldw = 2 * NKp; v.Y = ctx + (size_t) t0 * H * R; v.ldy = R; v.M = nq * H; v.N = R; v.K = 2 * NKp;
+    if (nq * H > 16) { v.X = (const float *) P; v.ldx = 2 * NKp; v.x_bf16 = 1; return pib_dense_mm(v, st); }
+    // a last block of very few rows goes to the row kernel, which reads fp32: widen the weights again
+    pib_launch(lat_widen_kernel, dim3((unsigned) (nq * H)), dim3(256), (size_t) 0, st, (const __nv_bfloat16 *) P, 2 * NKp, S);
+    CKL();
+    v.X = S; v.ldx = 2 * NKp;
     return pib_dense_mm(v, st);
 }
 
