@@ -269,7 +269,7 @@ int pib_dense_mm_tc(const pib_mm & a, cudaStream_t st) {
     const int  Kp = (a.K + 7) & ~7;
     const bool grouped = a.zrange != nullptr;
     const int  Zs = grouped ? 1 : a.Z;
-    if (a.x_bf16 && (grouped || a.xrows || a.Z != 1 || a.ldx % 8 || ((uintptr_t) a.X & 15))) return PIB_ERR_UNSUPP;
+    if (a.x_bf16 && (grouped || a.xrows || a.ldx % 8 || ((uintptr_t) a.X & 15) || (a.Z > 1 && a.xz % 8))) return PIB_ERR_UNSUPP;
     dt_scratch * sc = dt_scratch_of(st, a.x_bf16 ? 0 : (size_t) Zs * a.M * Kp * 2 + 256);
     if (!sc || (!a.x_bf16 && !sc->xs)) return PIB_ERR_UNSUPP;
     if (!a.x_bf16) pib_launch(dense_cast_kernel, dim3(dim3((unsigned) a.M, (unsigned) Zs)), dim3(128), (size_t) (0), st, a.X, a.ldx, a.xz, a.xrows, a.xdiv < 1 ? 1 : a.xdiv, a.M, a.K, Kp, sc->xs);
@@ -279,7 +279,7 @@ int pib_dense_mm_tc(const pib_mm & a, cudaStream_t st) {
     const int NB = per <= 32 ? 32 : per <= 64 ? 64 : 128;
     CUtensorMap wmap, xmap;
     int rc = dt_map3(&wmap, a.W, (uint64_t) a.K, (uint64_t) a.N, (uint64_t) a.Z, (uint64_t) a.ldw * 2, (uint64_t) (a.Z > 1 ? a.wz : (int64_t) a.N * a.ldw) * 2, DT_BM);
-    if (rc == PIB_OK && a.x_bf16) rc = dt_map3(&xmap, a.X, (uint64_t) a.K, (uint64_t) a.M, 1, (uint64_t) a.ldx * 2, (uint64_t) a.M * a.ldx * 2, (uint32_t) NB);
+    if (rc == PIB_OK && a.x_bf16) rc = dt_map3(&xmap, a.X, (uint64_t) a.K, (uint64_t) a.M, (uint64_t) a.Z, (uint64_t) a.ldx * 2, (uint64_t) (a.Z > 1 ? a.xz : (int64_t) a.M * a.ldx) * 2, (uint32_t) NB);
     else if (rc == PIB_OK) rc = dt_map3(&xmap, sc->xs, (uint64_t) Kp, (uint64_t) a.M, (uint64_t) Zs, (uint64_t) Kp * 2, (uint64_t) a.M * Kp * 2, (uint32_t) NB);
     if (rc != PIB_OK) return rc;
     switch (NB) {

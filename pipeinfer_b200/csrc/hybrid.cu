@@ -27,6 +27,7 @@ struct pib_hybrid_ctx {
     int cap = 0;
     float * x = nullptr, * h = nullptr, * y = nullptr, * proj = nullptr, * cq = nullptr, * q = nullptr, * qlat = nullptr, * lat = nullptr, * att = nullptr;
     float * rlog = nullptr, * wts = nullptr, * eup = nullptr, * edn = nullptr, * ysh = nullptr;
+    float * h2 = nullptr, * cv = nullptr, * vfirst = nullptr, * mixes = nullptr;   // parallel layers: second norm; convolved q | k | v; first mixing layer's values; token-shift mixes
     int32_t * ids = nullptr, * perm = nullptr, * inv = nullptr, * counts = nullptr, * offs = nullptr;
     // batch bookkeeping: pinned staging ring + device copy
     static const int RING = 4;
@@ -46,9 +47,13 @@ struct pib_hybrid_ctx {
 // kinds of launches, for the profile
 static const char * const HK_NAMES[] = { "cellmap", "embed_ln", "canon_conv", "mm_dq_dkv", "latent_prep", "mm_uq", "mm_absorb_uk", "latent_attention", "mm_uv", "mm_attn_o",
                                          "mm_qfv", "hgrn2_gates", "hgrn2_scan", "mm_hgrn2_o", "ln_residual", "mm_up", "polynorm", "mm_down", "mm_router", "moe_route",
-                                         "moe_sort", "mm_experts_up", "mm_experts_down", "mm_shared_up", "mm_shared_down", "moe_combine", "final_ln", "mm_head", "sample", "latent_attention_mm" };
+                                         "moe_sort", "mm_experts_up", "mm_experts_down", "mm_shared_up", "mm_shared_down", "moe_combine", "final_ln", "mm_head", "sample", "latent_attention_mm",
+                                         "embed_scale", "rms_norm_pair", "mm_qkv", "qkv_conv", "attn_prep", "kv_attention", "kv_attention_mm", "token_shift", "mm_rkvg", "mm_decay",
+                                         "decay_act", "wkv_scan", "delta_prep", "delta_scan", "gated_head_norm", "glu_clamp", "parallel_sum" };
 enum { HK_CELLMAP, HK_EMBED, HK_CANON, HK_DQKV, HK_LPREP, HK_UQ, HK_ABSORB, HK_LATTN, HK_UV, HK_AO, HK_QFV, HK_GATES, HK_SCAN, HK_HO, HK_LNRES, HK_UP, HK_POLY, HK_DOWN,
-       HK_ROUTER, HK_ROUTE, HK_SORT, HK_EUP, HK_EDOWN, HK_SUP, HK_SDOWN, HK_COMBINE, HK_FINAL, HK_HEAD, HK_SAMPLE, HK_LATTN_MM, HK_COUNT };
+       HK_ROUTER, HK_ROUTE, HK_SORT, HK_EUP, HK_EDOWN, HK_SUP, HK_SDOWN, HK_COMBINE, HK_FINAL, HK_HEAD, HK_SAMPLE, HK_LATTN_MM,
+       HK_EMBSCALE, HK_NORM2, HK_QKV, HK_QKVCONV, HK_APREP, HK_KVATTN, HK_KVATTN_MM, HK_SHIFT, HK_RKVG, HK_DECAY, HK_DECAYACT, HK_WKVSCAN, HK_DPREP, HK_DSCAN, HK_GHNORM, HK_GLU,
+       HK_PSUM, HK_COUNT };
 const char * pib_hybrid_kind_name(int k) { return k >= 0 && k < HK_COUNT ? HK_NAMES[k] : "?"; }
 
 // fetch and clear the records; returns the count (the stream is synchronised)
@@ -112,9 +117,11 @@ int pib_hybrid_slots_free(const pib_context * c) { return c->hy ? c->hy->slots.n
 
 static bool attn_mm_enabled() { static const int on = getenv("PIB_ATTN_MM") ? atoi(getenv("PIB_ATTN_MM")) : 1; return on != 0; }
 
-static int grow_attn_mm(pib_context * c, const pib_hlayer & L, int nq, int NK) {
+// operands of the matmul form of an attention: key rows of `kw` (+ `kx` extra) bfloat16 each, transposed values [kw][2 NKp], query and
+// score rows
+static int grow_attn_mm(pib_context * c, size_t kw, size_t kx, int q_rows, int s_rows, int NK) {
     pib_hybrid_ctx * x = c->hy;
-    const size_t R = (size_t) L.kv_rank, RK = R + (size_t) L.rot_dim, NKp = ((size_t) NK + 7) & ~(size_t) 7, rows = (size_t) nq * L.heads;
+    const size_t R = kw, RK = kw + kx, NKp = ((size_t) NK + 7) & ~(size_t) 7, rows = (size_t) s_rows;
     auto grow = [&](void ** p, size_t * cap, size_t need) {
         if (need <= *cap) return true;
         cudaStreamSynchronize(c->stream);
@@ -123,7 +130,7 @@ static int grow_attn_mm(pib_context * c, const pib_hlayer & L, int nq, int NK) {
         if (cudaMalloc(p, *cap) != cudaSuccess) { cudaGetLastError(); *p = nullptr; *cap = 0; return false; }
         return true;
     };
-    if (!grow(&x->am_kb, &x->am_kb_cap, NKp * RK * 2) || !grow(&x->am_vt, &x->am_vt_cap, R * NKp * 4) || !grow((void **) &x->am_q, &x->am_q_cap, rows * RK * 4) ||
+    if (!grow(&x->am_kb, &x->am_kb_cap, NKp * RK * 2) || !grow(&x->am_vt, &x->am_vt_cap, R * NKp * 4) || !grow((void **) &x->am_q, &x->am_q_cap, (size_t) q_rows * RK * 4) ||
         !grow((void **) &x->am_s, &x->am_s_cap, rows * NKp * 8) || !grow(&x->am_p, &x->am_p_cap, rows * NKp * 4)) { pib_set_error("decode: out of memory for the attention's score rows"); return PIB_ERR_NOMEM; }
     return PIB_OK;
 }
@@ -131,8 +138,9 @@ static int grow_attn_mm(pib_context * c, const pib_hlayer & L, int nq, int NK) {
 static void free_scratch(pib_hybrid_ctx * x) {
     for (void * b : { (void *) x->x, (void *) x->h, (void *) x->y, (void *) x->proj, (void *) x->cq, (void *) x->q, (void *) x->qlat, (void *) x->lat, (void *) x->att,
                       (void *) x->rlog, (void *) x->wts, (void *) x->eup, (void *) x->edn, (void *) x->ysh, (void *) x->ids, (void *) x->perm, (void *) x->inv,
-                      (void *) x->counts, (void *) x->offs }) if (b) cudaFree(b);
+                      (void *) x->counts, (void *) x->offs, (void *) x->h2, (void *) x->cv, (void *) x->vfirst, (void *) x->mixes }) if (b) cudaFree(b);
     x->x = x->h = x->y = x->proj = x->cq = x->q = x->qlat = x->lat = x->att = x->rlog = x->wts = x->eup = x->edn = x->ysh = nullptr;
+    x->h2 = x->cv = x->vfirst = x->mixes = nullptr;
     x->ids = x->perm = x->inv = x->counts = x->offs = nullptr;
     x->cap = 0;
 }
@@ -173,7 +181,8 @@ static int grow_scratch(pib_context * c, int T) {
                     fl(&x->qlat, (size_t) hy->w_lat) && fl(&x->lat, (size_t) hy->w_lat) && fl(&x->att, (size_t) hy->w_att) && fl(&x->rlog, (size_t) hy->w_router) &&
                     fl(&x->wts, (size_t) hy->w_pairs) && fl(&x->eup, (size_t) hy->w_eup) && fl(&x->edn, (size_t) hy->w_pairs * W) && fl(&x->ysh, hy->w_pairs ? W : 0) &&
                     in(&x->ids, n * hy->w_pairs) && in(&x->perm, n * hy->w_pairs) && in(&x->inv, n * hy->w_pairs) && in(&x->counts, (size_t) hy->w_router + 1) &&
-                    in(&x->offs, (size_t) hy->w_router + 2);
+                    in(&x->offs, (size_t) hy->w_router + 2) && fl(&x->h2, hy->form == PIB_FORM_PARALLEL ? W : 0) && fl(&x->cv, (size_t) hy->w_conv) &&
+                    fl(&x->vfirst, (size_t) hy->w_vfirst) && fl(&x->mixes, (size_t) hy->w_shift);
     if (!ok) { cudaGetLastError(); free_scratch(x); pib_set_error("decode: out of memory for the work buffers of %d tokens", T); return PIB_ERR_NOMEM; }
     x->cap = (int) n;
     return PIB_OK;
@@ -187,7 +196,6 @@ static int grow_scratch(pib_context * c, int T) {
 #define MM_ATTN_BLOCK   512
 struct pib_hseg { int start, len, seq, slot; bool fresh; };
 
-static int grow_attn_mm(pib_context * c, const pib_hlayer & L, int nq, int NK);
 
 static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B, const int32_t * B_pos_host, const std::vector<pib_hseg> & segs) {
     pib_hybrid_ctx *   x  = c->hy;
@@ -219,85 +227,198 @@ static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B, cons
         a.exact = exact || w->type == PIB_TYPE_F32;
         return pib_dense_mm(a, st);
     };
+    // ---- mixers: read hin [T][W], leave their output in x->y ----
+    auto mixer_latent = [&](const pib_hlayer & L, const float * hin) -> int {
+        const int H = L.heads, D = L.dim, rd = L.rot_dim, R = L.kv_rank, V = L.vdim, ldp = (int) L.dqkv->N, row = hy->cache_row[L.cache_id];
+        float * cache = x->cache[L.cache_id];
+        const double keys = key_pairs(L.window);
+        RC(HK_DQKV, mmfl(L.dqkv), mmby(L.dqkv), mm(L.dqkv, hin, W, x->proj, ldp, PIB_EPI_NONE));
+        RC(HK_LPREP, 0, 8.0 * Td * ldp, pib_latent_prep(x->proj, ldp, L, L.dq_norm, L.dkv_norm, eps, B, x->rope[L.rope_id], (int) c->n_ctx, x->cq, L.kv_from < 0 ? cache : nullptr, row, st));
+        RC(HK_UQ, mmfl(L.uq), mmby(L.uq), mm(L.uq, x->cq, L.q_rank, x->q, H * (D + rd), PIB_EPI_NONE));
+        {   // q_lat[t][h] = W_uk,h^T q_unrotated[t][h]: one problem per head
+            pib_mm a;
+            a.W = L.ukT->base; a.wtype = L.ukT->type; a.ldw = D; a.wz = (int64_t) R * D; a.X = x->q; a.ldx = (int64_t) H * (D + rd); a.xz = D + rd;
+            a.Y = x->qlat; a.ldy = (int64_t) H * R; a.yz = R; a.M = T; a.N = R; a.K = D; a.Z = H; a.exact = exact;
+            RC(HK_ABSORB, 2.0 * Td * H * R * D, wbytes(L.ukT) + 4.0 * Td * H * (D + R), pib_dense_mm(a, st));
+        }
+        const bool mm_ok = !exact && row >= MM_ATTN_MIN_ROW && row % 8 == 0 && attn_mm_enabled();
+        bool any_mm = false, any_simt = false;
+        for (const pib_hseg & g : segs) { if (mm_ok && g.len >= MM_ATTN_MIN_LEN) any_mm = true; else any_simt = true; }
+        if (any_simt)
+            RC(HK_LATTN, 4.0 * keys * H * (R + rd), 4.0 * keys * (R + rd) + 8.0 * Td * H * R,
+               pib_latent_attention(x->q, x->qlat, L, B, x->rope[L.rope_id], (int) c->n_ctx, cache, row, x->cellmap, (int) c->n_ctx, x->lat, any_mm ? B.mmflag : nullptr, st));
+        for (const pib_hseg & g : segs) {
+            if (!mm_ok || g.len < MM_ATTN_MIN_LEN) continue;
+            for (int o = 0; o < g.len; o += MM_ATTN_BLOCK) {
+                const int nq = std::min(MM_ATTN_BLOCK, g.len - o), p0 = B_pos_host[g.start + o];
+                const int j0 = std::max(0, p0 - L.window + 1), NK = p0 + nq - j0;
+                if ((rc = grow_attn_mm(c, (size_t) R, (size_t) L.rot_dim, nq * H, nq * H, NK)) != PIB_OK) return rc;
+                RC(HK_LATTN_MM, 2.0 * nq * H * (double) NK * (2.0 * R + rd), 2.0 * NK * (2.0 * R + rd) + 8.0 * nq * H * (2.0 * R + rd) + 8.0 * nq * H * (double) NK,
+                   pib_latent_attention_mm(x->q, x->qlat, L, B, x->rope[L.rope_id], cache, row, x->cellmap + (size_t) g.slot * c->n_ctx, g.start + o, nq, j0, NK,
+                                           x->am_kb, x->am_vt, x->am_q, x->am_s, x->am_p, x->lat, st));
+                nk += 5;
+            }
+        }
+        {   // value of head h = W_uv,h (sum_j p_j c_j)
+            pib_mm a;
+            a.W = L.uv->base; a.wtype = L.uv->type; a.ldw = R; a.wz = (int64_t) V * R; a.X = x->lat; a.ldx = (int64_t) H * R; a.xz = R;
+            a.Y = x->att; a.ldy = (int64_t) H * V; a.yz = V; a.M = T; a.N = V; a.K = R; a.Z = H; a.exact = exact;
+            RC(HK_UV, 2.0 * Td * H * R * V, wbytes(L.uv) + 4.0 * Td * H * (V + R), pib_dense_mm(a, st));
+        }
+        RC(HK_AO, mmfl(L.wo), mmby(L.wo), mm(L.wo, x->att, H * V, x->y, W, PIB_EPI_NONE));
+        return PIB_OK;
+    };
+    auto mixer_hgrn2 = [&](const pib_hlayer & L, const float * hin) -> int {
+        const int H = L.heads, HD = H * L.dim, ldp = (int) L.qfv->N;
+        RC(HK_QFV, mmfl(L.qfv), mmby(L.qfv), mm(L.qfv, hin, W, x->proj, ldp, PIB_EPI_NONE));
+        RC(HK_GATES, 0, 16.0 * Td * HD, pib_hgrn2_gates(x->proj, ldp, L.f_bias, L.lower, T, HD, st));
+        RC(HK_SCAN, 5.0 * Td * HD * L.vdim, 4.0 * Td * ldp + 8.0 * Td * H * L.vdim, pib_hgrn2_scan(x->proj, ldp, L, B, x->state, hy->state_floats, L.onorm, eps, x->att, st)); nk++;
+        RC(HK_HO, mmfl(L.wo), mmby(L.wo), mm(L.wo, x->att, H * L.vdim, x->y, W, PIB_EPI_NONE));
+        return PIB_OK;
+    };
+    // windowed attention over cached key / value heads: projections, convolution, norms + value mixing + cache write, attention, output
+    auto mixer_swa = [&](const pib_hlayer & L, const float * hin) -> int {
+        const int H = L.heads, G = L.kv_heads, D = L.dim, V = L.vdim, C = (int) L.qkv->N, row = hy->cache_row[L.cache_id];
+        float * cache = x->cache[L.cache_id];
+        const double keys = key_pairs(L.window);
+        RC(HK_QKV, mmfl(L.qkv), mmby(L.qkv), mm(L.qkv, hin, W, x->proj, C, PIB_EPI_NONE));
+        const float * src = x->proj;
+        if (L.conv) {
+            RC(HK_QKVCONV, 2.0 * Td * C * L.taps, 8.0 * Td * C, pib_chan_conv(x->proj, C, L.conv, L.taps, B, x->state, hy->state_floats, L.tail_off, C, x->cv, C, 0, 0, st));
+            nk += L.taps > 1;
+            src = x->cv;
+        }
+        RC(HK_APREP, 0, 8.0 * Td * C, pib_swa_prep(src, C, L, eps, B, x->q, cache, row, x->vfirst, st));
+        const bool mm_ok = !exact && D % 8 == 0 && D >= 16 && V >= 16 && attn_mm_enabled();
+        bool any_mm = false, any_simt = false;
+        for (const pib_hseg & g : segs) { if (mm_ok && g.len >= MM_ATTN_MIN_LEN) any_mm = true; else any_simt = true; }
+        if (any_simt)
+            RC(HK_KVATTN, 2.0 * keys * H * (D + V), 4.0 * keys * G * (D + V) + 4.0 * Td * H * (D + V),
+               pib_kv_attention(x->q, L, B, cache, row, x->cellmap, (int) c->n_ctx, x->att, any_mm ? B.mmflag : nullptr, st));
+        for (const pib_hseg & g : segs) {
+            if (!mm_ok || g.len < MM_ATTN_MIN_LEN) continue;
+            const int nb = (g.len + MM_ATTN_BLOCK - 1) / MM_ATTN_BLOCK, per = (g.len + nb - 1) / nb;      // blocks of equal size: none is left with a handful of rows
+            for (int o = 0; o < g.len; o += per) {
+                const int nq = std::min(per, g.len - o), p0 = B_pos_host[g.start + o];
+                const int j0 = std::max(0, p0 - L.window + 1), NK = p0 + nq - j0;
+                if ((rc = grow_attn_mm(c, (size_t) G * std::max(D, V), 0, nq * H, nq * H, NK)) != PIB_OK) return rc;
+                RC(HK_KVATTN_MM, 2.0 * nq * H * (double) NK * (D + 2.0 * V), 2.0 * NK * G * (D + 2.0 * V) + 8.0 * nq * H * (D + V) + 8.0 * nq * H * (double) NK,
+                   pib_kv_attention_mm(x->q, L, B, cache, row, x->cellmap + (size_t) g.slot * c->n_ctx, g.start + o, nq, j0, NK, x->am_kb, x->am_vt, x->am_q, x->am_s, x->am_p,
+                                       x->att, st));
+                nk += 5;
+            }
+        }
+        RC(HK_AO, mmfl(L.wo), mmby(L.wo), mm(L.wo, x->att, H * V, x->y, W, PIB_EPI_NONE));
+        return PIB_OK;
+    };
+    // RWKV-style time mixing: the five token-shift mixes, r | k | v | g as four problems of one launch, the decay's two small matmuls, the recurrence
+    auto mixer_wkv = [&](const pib_hlayer & L, const float * hin) -> int {
+        const int H = L.heads, D = L.dim, HD = H * D, R = L.w_rank;
+        RC(HK_SHIFT, 10.0 * Td * Wd, 24.0 * Td * Wd, pib_token_shift(hin, L.mu, 5, B, x->state, hy->state_floats, L.shift_off, W, x->mixes, st)); nk++;
+        {
+            pib_mm a;
+            a.W = L.rkvg->base; a.wtype = L.rkvg->type; a.ldw = W; a.wz = (int64_t) HD * W; a.X = x->mixes; a.ldx = 5 * (int64_t) W; a.xz = W;
+            a.Y = x->proj; a.ldy = 4 * (int64_t) HD; a.yz = HD; a.M = T; a.N = HD; a.K = W; a.Z = 4; a.exact = exact;
+            RC(HK_RKVG, mmfl(L.rkvg), mmby(L.rkvg), pib_dense_mm(a, st));
+        }
+        RC(HK_DECAY, mmfl(L.w1), mmby(L.w1), mm(L.w1, x->mixes + 4 * (size_t) W, 5 * W, x->cq, R, PIB_EPI_NONE));
+        RC(HK_DECAYACT, 0, 8.0 * Td * R, pib_rows_act(x->cq, R, R, T, 0, nullptr, st));
+        RC(HK_DECAY, mmfl(L.w2), mmby(L.w2), mm(L.w2, x->cq, R, x->lat, HD, PIB_EPI_NONE));
+        RC(HK_DECAYACT, 0, 8.0 * Td * HD, pib_rows_act(x->lat, HD, HD, T, 1, L.w0, st));
+        RC(HK_WKVSCAN, 7.0 * Td * HD * D, 4.0 * Td * 5 * HD, pib_wkv_scan(x->proj, 4 * HD, x->lat, HD, L, B, x->state, hy->state_floats, x->att, st));
+        RC(HK_GHNORM, 0, 12.0 * Td * HD, pib_gated_head_norm(x->att, T, H, D, L.onorm, D, x->proj + 3 * (size_t) HD, 4 * HD, eps, st));
+        RC(HK_HO, mmfl(L.wo), mmby(L.wo), mm(L.wo, x->att, HD, x->y, W, PIB_EPI_NONE));
+        return PIB_OK;
+    };
+    // gated delta rule: q | k | v | gate | beta | decay logits in one matmul, convolution + silu, unit vectors and gates, the recurrence
+    auto mixer_delta = [&](const pib_hlayer & L, const float * hin) -> int {
+        const int H = L.heads, G = L.kv_heads, D = L.dim, V = L.vdim, C = 2 * G * D + H * V, N = (int) L.qkv->N, b_off = C + H * V, a_off = b_off + H;
+        RC(HK_QKV, mmfl(L.qkv), mmby(L.qkv), mm(L.qkv, hin, W, x->proj, N, PIB_EPI_NONE));
+        RC(HK_QKVCONV, 2.0 * Td * C * L.taps, 8.0 * Td * C, pib_chan_conv(x->proj, N, L.conv, L.taps, B, x->state, hy->state_floats, L.tail_off, C, x->cv, C, 0, 1, st));
+        nk += L.taps > 1;
+        RC(HK_DPREP, 0, 8.0 * Td * 2 * G * D, pib_delta_prep(x->cv, C, L, x->proj, N, b_off, a_off, x->cq, T, st));
+        RC(HK_DSCAN, 8.0 * Td * H * D * V, 4.0 * Td * (C + 2.0 * H + H * V), pib_delta_scan(x->cv, C, x->cq, L, B, x->state, hy->state_floats, x->att, st));
+        RC(HK_GHNORM, 0, 12.0 * Td * H * V, pib_gated_head_norm(x->att, T, H, V, L.onorm, 0, x->proj + C, N, eps, st));
+        RC(HK_HO, mmfl(L.wo), mmby(L.wo), mm(L.wo, x->att, H * V, x->y, W, PIB_EPI_NONE));
+        return PIB_OK;
+    };
+    auto run_mixer = [&](const pib_hlayer & L, const float * hin) -> int {
+        switch (L.mixer) {
+            case PIB_MIXER_LATENT: return mixer_latent(L, hin);
+            case PIB_MIXER_HGRN2:  return mixer_hgrn2(L, hin);
+            case PIB_MIXER_SWA:    return mixer_swa(L, hin);
+            case PIB_MIXER_WKV:    return mixer_wkv(L, hin);
+            case PIB_MIXER_DELTA:  return mixer_delta(L, hin);
+        }
+        pib_set_error("decode: mixer %d", L.mixer);
+        return PIB_ERR_UNSUPP;
+    };
+    // routed experts + shared expert of `min` [T][W]: x->edn holds the experts' outputs per (token, expert) pair in sorted order, x->ysh the
+    // shared expert's; the caller combines them.  relu^2 experts: up rows only, the weights multiply the outputs (moe_combine); clamped gated
+    // experts: rows gate | up, the router's weight multiplies the expert's input, i.e. both products before the clamp (glu_clamp)
+    auto run_experts = [&](const pib_hlayer & L, const float * min, int * ld_shared) -> int {
+        const int E = L.n_experts, top = L.top, P = T * top, glu = L.expert == PIB_EXPERT_GLU_CLAMP, NU = (glu ? 2 : 1) * L.ff_e;
+        const double touched = P >= E ? 1.0 : (double) P / E;          // weights of experts without a row are not read
+        RC(HK_ROUTER, mmfl(L.router), mmby(L.router), mm(L.router, min, W, x->rlog, E, PIB_EPI_NONE));
+        RC(HK_ROUTE, 0, 4.0 * Td * E, pib_moe_route(x->rlog, T, E, top, L.route, x->ids, x->wts, st));
+        RC(HK_SORT, 0, 4.0 * P * (E + 3.0), pib_moe_sort(x->ids, P, E, x->counts, x->offs, x->perm, x->inv, st)); nk++;
+        {   // up-projection of every (token, expert) pair, pairs grouped by expert
+            pib_mm a;
+            a.W = L.e_up->base; a.wtype = L.e_up->type; a.ldw = W; a.wz = (int64_t) NU * W; a.X = min; a.ldx = W; a.xrows = x->perm; a.xdiv = top;
+            a.Y = x->eup; a.ldy = NU; a.M = P; a.N = NU; a.K = W; a.Z = E; a.zrange = x->offs; a.epi = glu ? PIB_EPI_NONE : PIB_EPI_RELU2; a.exact = exact;
+            RC(HK_EUP, 2.0 * P * NU * Wd, wbytes(L.e_up) * touched + 4.0 * P * (Wd + NU), pib_dense_mm(a, st));
+            if (glu) RC(HK_GLU, 0, 12.0 * P * L.ff_e, pib_glu_clamp(x->eup, NU, L.ff_e, L.limit_e, x->wts, x->perm, P, st));
+            pib_mm b;
+            b.W = L.e_down->base; b.wtype = L.e_down->type; b.ldw = L.ff_e; b.wz = (int64_t) W * L.ff_e; b.X = x->eup; b.ldx = NU;
+            b.Y = x->edn; b.ldy = W; b.M = P; b.N = W; b.K = L.ff_e; b.Z = E; b.zrange = x->offs; b.exact = exact;
+            RC(HK_EDOWN, 2.0 * P * L.ff_e * Wd, wbytes(L.e_down) * touched + 4.0 * P * (Wd + L.ff_e), pib_dense_mm(b, st));
+        }
+        if (L.s_up) {
+            const int NS = (int) L.s_up->N, ld = (NS + 3) & ~3;
+            *ld_shared = ld;
+            RC(HK_SUP, mmfl(L.s_up), mmby(L.s_up), mm(L.s_up, min, W, x->proj, ld, glu ? PIB_EPI_NONE : PIB_EPI_RELU2));
+            if (glu) RC(HK_GLU, 0, 12.0 * Td * L.ff_s, pib_glu_clamp(x->proj, ld, L.ff_s, L.limit_s, nullptr, nullptr, T, st));
+            pib_mm d;
+            d.W = L.s_down->base; d.wtype = L.s_down->type; d.ldw = L.ff_s; d.X = x->proj; d.ldx = ld; d.Y = x->ysh; d.ldy = W; d.M = T; d.N = W; d.K = L.ff_s;
+            d.exact = exact || L.s_down->type == PIB_TYPE_F32;
+            RC(HK_SDOWN, mmfl(L.s_down), mmby(L.s_down), pib_dense_mm(d, st));
+        }
+        return PIB_OK;
+    };
+
     RC(HK_CELLMAP, 0, 16.0 * Td, pib_cellmap_set(x->cellmap, (int) c->n_ctx, B, st));
-    RC(HK_EMBED, 0, 6.0 * Td * Wd, pib_embed_ln(m->tok_embd, B.tok, hy->embd_norm, eps, T, W, x->x, st));
+    if (hy->form == PIB_FORM_PARALLEL) RC(HK_EMBSCALE, 0, 6.0 * Td * Wd, pib_embed_scale(m->tok_embd, B.tok, hy->embd_scale, T, W, x->x, st));
+    else                               RC(HK_EMBED, 0, 6.0 * Td * Wd, pib_embed_ln(m->tok_embd, B.tok, hy->embd_norm, eps, T, W, x->x, st));
     for (int il = 0; il < m->n_layer; il++) {
         const pib_hlayer & L = hy->layers[il];
-        const float * hin = x->x;
-        if (L.canon) { RC(HK_CANON, 2.0 * Td * Wd * hy->taps, 8.0 * Td * Wd, pib_canon_conv(x->x, L.canon, hy->taps, B, x->state, hy->state_floats, L.tail_off, W, x->h, st)); nk += hy->taps > 1; hin = x->h; }
-        if (L.mixer == PIB_MIXER_LATENT) {
-            const int H = L.heads, D = L.dim, rd = L.rot_dim, R = L.kv_rank, V = L.vdim, ldp = (int) L.dqkv->N, row = hy->cache_row[L.cache_id];
-            float * cache = x->cache[L.cache_id];
-            const double keys = key_pairs(L.window);
-            RC(HK_DQKV, mmfl(L.dqkv), mmby(L.dqkv), mm(L.dqkv, hin, W, x->proj, ldp, PIB_EPI_NONE));
-            RC(HK_LPREP, 0, 8.0 * Td * ldp, pib_latent_prep(x->proj, ldp, L, L.dq_norm, L.dkv_norm, eps, B, x->rope[L.rope_id], (int) c->n_ctx, x->cq, L.kv_from < 0 ? cache : nullptr, row, st));
-            RC(HK_UQ, mmfl(L.uq), mmby(L.uq), mm(L.uq, x->cq, L.q_rank, x->q, H * (D + rd), PIB_EPI_NONE));
-            {   // q_lat[t][h] = W_uk,h^T q_unrotated[t][h]: one problem per head
-                pib_mm a;
-                a.W = L.ukT->base; a.wtype = L.ukT->type; a.ldw = D; a.wz = (int64_t) R * D; a.X = x->q; a.ldx = (int64_t) H * (D + rd); a.xz = D + rd;
-                a.Y = x->qlat; a.ldy = (int64_t) H * R; a.yz = R; a.M = T; a.N = R; a.K = D; a.Z = H; a.exact = exact;
-                RC(HK_ABSORB, 2.0 * Td * H * R * D, wbytes(L.ukT) + 4.0 * Td * H * (D + R), pib_dense_mm(a, st));
-            }
-            const bool mm_ok = !exact && row >= MM_ATTN_MIN_ROW && row % 8 == 0 && attn_mm_enabled();
-            bool any_mm = false, any_simt = false;
-            for (const pib_hseg & g : segs) { if (mm_ok && g.len >= MM_ATTN_MIN_LEN) any_mm = true; else any_simt = true; }
-            if (any_simt)
-                RC(HK_LATTN, 4.0 * keys * H * (R + rd), 4.0 * keys * (R + rd) + 8.0 * Td * H * R,
-                   pib_latent_attention(x->q, x->qlat, L, B, x->rope[L.rope_id], (int) c->n_ctx, cache, row, x->cellmap, (int) c->n_ctx, x->lat, any_mm ? B.mmflag : nullptr, st));
-            for (const pib_hseg & g : segs) {
-                if (!mm_ok || g.len < MM_ATTN_MIN_LEN) continue;
-                for (int o = 0; o < g.len; o += MM_ATTN_BLOCK) {
-                    const int nq = std::min(MM_ATTN_BLOCK, g.len - o), p0 = B_pos_host[g.start + o];
-                    const int j0 = std::max(0, p0 - L.window + 1), NK = p0 + nq - j0;
-                    if ((rc = grow_attn_mm(c, L, nq, NK)) != PIB_OK) return rc;
-                    RC(HK_LATTN_MM, 2.0 * nq * H * (double) NK * (2.0 * R + rd), 2.0 * NK * (2.0 * R + rd) + 8.0 * nq * H * (2.0 * R + rd) + 8.0 * nq * H * (double) NK,
-                       pib_latent_attention_mm(x->q, x->qlat, L, B, x->rope[L.rope_id], cache, row, x->cellmap + (size_t) g.slot * c->n_ctx, g.start + o, nq, j0, NK,
-                                               x->am_kb, x->am_vt, x->am_q, x->am_s, x->am_p, x->lat, st));
-                    nk += 5;
-                }
-            }
-            {   // value of head h = W_uv,h (sum_j p_j c_j)
-                pib_mm a;
-                a.W = L.uv->base; a.wtype = L.uv->type; a.ldw = R; a.wz = (int64_t) V * R; a.X = x->lat; a.ldx = (int64_t) H * R; a.xz = R;
-                a.Y = x->att; a.ldy = (int64_t) H * V; a.yz = V; a.M = T; a.N = V; a.K = R; a.Z = H; a.exact = exact;
-                RC(HK_UV, 2.0 * Td * H * R * V, wbytes(L.uv) + 4.0 * Td * H * (V + R), pib_dense_mm(a, st));
-            }
-            RC(HK_AO, mmfl(L.wo), mmby(L.wo), mm(L.wo, x->att, H * V, x->y, W, PIB_EPI_NONE));
+        int lds = 0;
+        if (hy->form == PIB_FORM_PARALLEL) {
+            // x += mixer(N1 x) + ff(N2 x): both norms in one pass over x, the sum in one pass at the end
+            RC(HK_NORM2, 0, (L.mlp ? 12.0 : 8.0) * Td * Wd, pib_rms_norm2(x->x, L.norm1, L.mlp ? L.norm2 : nullptr, eps, 1.0f, T, W, x->h, x->h2, st));
+            if ((rc = run_mixer(L, x->h)) != PIB_OK) return rc;
+            if (L.mlp == PIB_MLP_MOE) {
+                if ((rc = run_experts(L, x->h2, &lds)) != PIB_OK) return rc;
+                if (L.expert != PIB_EXPERT_GLU_CLAMP) { pib_set_error("decode: parallel layers take experts whose weights multiply their inputs"); return PIB_ERR_UNSUPP; }
+                RC(HK_PSUM, 2.0 * Td * L.top * Wd, 4.0 * Wd * Td * (L.top + 4.0),
+                   pib_parallel_sum(x->x, x->y, L.s_up ? x->ysh : nullptr, L.s_gate ? x->proj + 2 * (size_t) L.ff_s : nullptr, lds, x->edn, x->inv, L.top, T, W, st));
+            } else if (L.mlp == PIB_MLP_NONE) {
+                RC(HK_PSUM, 0, 12.0 * Wd * Td, pib_parallel_sum(x->x, x->y, nullptr, nullptr, 0, nullptr, nullptr, 0, T, W, st));
+            } else { pib_set_error("decode: feed-forward %d in a parallel layer", L.mlp); return PIB_ERR_UNSUPP; }
         } else {
-            const int H = L.heads, HD = H * L.dim, ldp = (int) L.qfv->N;
-            RC(HK_QFV, mmfl(L.qfv), mmby(L.qfv), mm(L.qfv, hin, W, x->proj, ldp, PIB_EPI_NONE));
-            RC(HK_GATES, 0, 16.0 * Td * HD, pib_hgrn2_gates(x->proj, ldp, L.f_bias, L.lower, T, HD, st));
-            RC(HK_SCAN, 5.0 * Td * HD * L.vdim, 4.0 * Td * ldp + 8.0 * Td * H * L.vdim, pib_hgrn2_scan(x->proj, ldp, L, B, x->state, hy->state_floats, L.onorm, eps, x->att, st)); nk++;
-            RC(HK_HO, mmfl(L.wo), mmby(L.wo), mm(L.wo, x->att, H * L.vdim, x->y, W, PIB_EPI_NONE));
-        }
-        RC(HK_LNRES, 0, 12.0 * Td * Wd, pib_layer_norm(x->y, L.norm1, eps, T, W, x->x, 1, st));
-        if (L.mlp == PIB_MLP_POLYNORM) {
-            RC(HK_UP, mmfl(L.up), mmby(L.up), mm(L.up, x->x, W, x->proj, L.ff, PIB_EPI_NONE));
-            RC(HK_POLY, 0, 8.0 * Td * L.ff, pib_polynorm(x->proj, T, L.ff, L.act, eps, st));
-            RC(HK_DOWN, mmfl(L.down), mmby(L.down), mm(L.down, x->proj, L.ff, x->y, W, PIB_EPI_NONE));
-            RC(HK_LNRES, 0, 12.0 * Td * Wd, pib_layer_norm(x->y, L.norm2, eps, T, W, x->x, 1, st));
-        } else if (L.mlp == PIB_MLP_MOE) {
-            const int E = L.n_experts, top = L.top, P = T * top;
-            const double touched = P >= E ? 1.0 : (double) P / E;          // weights of experts without a row are not read
-            RC(HK_ROUTER, mmfl(L.router), mmby(L.router), mm(L.router, x->x, W, x->rlog, E, PIB_EPI_NONE));
-            RC(HK_ROUTE, 0, 4.0 * Td * E, pib_moe_route(x->rlog, T, E, top, x->ids, x->wts, st));
-            RC(HK_SORT, 0, 4.0 * P * (E + 3.0), pib_moe_sort(x->ids, P, E, x->counts, x->offs, x->perm, x->inv, st)); nk++;
-            {   // up-projection of every (token, expert) pair, pairs grouped by expert; relu^2 on the way out
-                pib_mm a;
-                a.W = L.e_up->base; a.wtype = L.e_up->type; a.ldw = W; a.wz = (int64_t) L.ff_e * W; a.X = x->x; a.ldx = W; a.xrows = x->perm; a.xdiv = top;
-                a.Y = x->eup; a.ldy = L.ff_e; a.M = P; a.N = L.ff_e; a.K = W; a.Z = E; a.zrange = x->offs; a.epi = PIB_EPI_RELU2; a.exact = exact;
-                RC(HK_EUP, 2.0 * P * L.ff_e * Wd, wbytes(L.e_up) * touched + 4.0 * P * (Wd + L.ff_e), pib_dense_mm(a, st));
-                pib_mm b;
-                b.W = L.e_down->base; b.wtype = L.e_down->type; b.ldw = L.ff_e; b.wz = (int64_t) W * L.ff_e; b.X = x->eup; b.ldx = L.ff_e;
-                b.Y = x->edn; b.ldy = W; b.M = P; b.N = W; b.K = L.ff_e; b.Z = E; b.zrange = x->offs; b.exact = exact;
-                RC(HK_EDOWN, 2.0 * P * L.ff_e * Wd, wbytes(L.e_down) * touched + 4.0 * P * (Wd + L.ff_e), pib_dense_mm(b, st));
+            const float * hin = x->x;
+            if (L.canon) { RC(HK_CANON, 2.0 * Td * Wd * hy->taps, 8.0 * Td * Wd, pib_canon_conv(x->x, L.canon, hy->taps, B, x->state, hy->state_floats, L.tail_off, W, x->h, st)); nk += hy->taps > 1; hin = x->h; }
+            if ((rc = run_mixer(L, hin)) != PIB_OK) return rc;
+            RC(HK_LNRES, 0, 12.0 * Td * Wd, pib_layer_norm(x->y, L.norm1, eps, T, W, x->x, 1, st));
+            if (L.mlp == PIB_MLP_POLYNORM) {
+                RC(HK_UP, mmfl(L.up), mmby(L.up), mm(L.up, x->x, W, x->proj, L.ff, PIB_EPI_NONE));
+                RC(HK_POLY, 0, 8.0 * Td * L.ff, pib_polynorm(x->proj, T, L.ff, L.act, eps, st));
+                RC(HK_DOWN, mmfl(L.down), mmby(L.down), mm(L.down, x->proj, L.ff, x->y, W, PIB_EPI_NONE));
+                RC(HK_LNRES, 0, 12.0 * Td * Wd, pib_layer_norm(x->y, L.norm2, eps, T, W, x->x, 1, st));
+            } else if (L.mlp == PIB_MLP_MOE) {
+                if ((rc = run_experts(L, x->x, &lds)) != PIB_OK) return rc;
+                RC(HK_COMBINE, 2.0 * Td * L.top * Wd, 4.0 * Wd * Td * (L.top + 2.0), pib_moe_combine(L.s_up ? x->ysh : nullptr, x->edn, x->wts, x->inv, T, L.top, W, x->y, st));
+                RC(HK_LNRES, 0, 12.0 * Td * Wd, pib_layer_norm(x->y, L.norm2, eps, T, W, x->x, 1, st));
             }
-            if (L.s_up) {
-                RC(HK_SUP, mmfl(L.s_up), mmby(L.s_up), mm(L.s_up, x->x, W, x->proj, L.ff_s, PIB_EPI_RELU2));
-                RC(HK_SDOWN, mmfl(L.s_down), mmby(L.s_down), mm(L.s_down, x->proj, L.ff_s, x->ysh, W, PIB_EPI_NONE));
-            }
-            RC(HK_COMBINE, 2.0 * P * Wd, 4.0 * Wd * (P + 2.0 * Td), pib_moe_combine(L.s_up ? x->ysh : nullptr, x->edn, x->wts, x->inv, T, top, W, x->y, st));
-            RC(HK_LNRES, 0, 12.0 * Td * Wd, pib_layer_norm(x->y, L.norm2, eps, T, W, x->x, 1, st));
         }
         if (const char * dump = getenv("PIB_HYBRID_DUMP")) {          // debugging: the residual stream after every layer, one file per layer and decode
             std::vector<float> hb((size_t) T * W);
@@ -308,7 +429,8 @@ static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B, cons
             if (FILE * f = fopen(path, "wb")) { fwrite(hb.data(), 4, hb.size(), f); fclose(f); }
         }
     }
-    RC(HK_FINAL, 0, 8.0 * Td * Wd, pib_layer_norm(x->x, m->output_norm, eps, T, W, x->h, 0, st));
+    if (hy->form == PIB_FORM_PARALLEL) RC(HK_FINAL, 0, 8.0 * Td * Wd, pib_rms_norm2(x->x, m->output_norm, nullptr, eps, hy->logit_scale, T, W, x->h, nullptr, st));
+    else                               RC(HK_FINAL, 0, 8.0 * Td * Wd, pib_layer_norm(x->x, m->output_norm, eps, T, W, x->h, 0, st));
     RC(HK_HEAD, mmfl(m->output), mmby(m->output), mm(m->output, x->h, W, run.logits, m->n_vocab, PIB_EPI_NONE));
     RC(HK_SAMPLE, 0, 4.0 * Td * m->n_vocab, pib_sample_topk(run.logits, T, m->n_vocab, c->bias_ids_dev, c->bias_val_dev, c->n_bias, run.res_dev, c->desc_dev, c->cancel_table, st));
 #undef RC

@@ -1,6 +1,12 @@
-// hybrid.cuh -- layer-list models: every layer names its own mixer (windowed latent attention with a sink, or the gated linear
-// recurrence HGRN2) and its own feed-forward (dense with a PolyNorm activation, or a routed mixture of experts with a shared expert).
-// The first design built from these parts is "Rapisun"; the parts take their sizes and constants as parameters so that another
+// hybrid.cuh -- layer-list models: every layer names its own mixer and its own feed-forward.
+//   mixers:        windowed latent attention with a sink; the gated linear recurrence HGRN2; windowed softmax attention over cached
+//                  key / value heads (grouped queries, short convolutions on q / k / v, per-head query / key norms, value mixing with
+//                  an earlier layer); RWKV-style time mixing (token shift, per-channel decay, bonus for the current token); the gated
+//                  delta rule
+//   feed-forwards: dense with a PolyNorm activation; routed mixtures of experts with a shared expert (softmax or sigmoid router,
+//                  weights renormalised or not, on the experts' outputs or inputs, relu^2 or clamped gated experts)
+//   layer forms:   sequential with LayerNorm on the sublayers' outputs; parallel with two RMS norms of the same input
+// Designs built from these parts: "Rapisun", "Fabivik".  The parts take their sizes and constants as parameters so that another
 // layer-list design can name them too.
 //
 // What such a model adds to the runtime, beside what llama / falcon graphs use:
@@ -14,9 +20,14 @@
 
 #include "engine.cuh"
 
-enum { PIB_MIXER_LATENT = 1, PIB_MIXER_HGRN2 = 2 };
+enum { PIB_MIXER_LATENT = 1, PIB_MIXER_HGRN2 = 2, PIB_MIXER_SWA = 3, PIB_MIXER_WKV = 4, PIB_MIXER_DELTA = 5 };
 enum { PIB_MLP_NONE = 0, PIB_MLP_POLYNORM = 1, PIB_MLP_MOE = 2 };
 enum { PIB_EPI_NONE = 0, PIB_EPI_RELU2 = 1 };
+// layer forms: x += LN(mixer(conv(x))), x += LN(ff(x))   |   x += mixer(N1(x)) + ff(N2(x)), N = RMS norm with weight (1 + w)
+enum { PIB_FORM_POSTNORM = 0, PIB_FORM_PARALLEL = 1 };
+// mixture of experts: how the router's logits become weights, where a weight multiplies, what an expert computes
+enum { PIB_ROUTE_SOFTMAX_RENORM = 0, PIB_ROUTE_SIGMOID = 1 };
+enum { PIB_EXPERT_RELU2 = 0, PIB_EXPERT_GLU_CLAMP = 1 };
 
 struct pib_hlayer {
     int     mixer = 0, mlp = 0;
@@ -36,6 +47,21 @@ struct pib_hlayer {
     float * f_bias = nullptr, * lower = nullptr, * onorm = nullptr;
     size_t  state_off = 0;                            // floats into a slot's state: the recurrent matrices [heads][dim][vdim]
     size_t  tail_off = 0;                             // floats into a slot's state: the convolution's last taps-1 inputs [taps-1][width]
+    // ---- windowed attention over cached key / value heads (PIB_MIXER_SWA): heads query heads share kv_heads key / value heads ----
+    int   kv_heads = 0, taps = 0, v_mix = 0;          // taps: of the convolution on q | k | v (0: none); v_mix 1: the first mixing layer (its values are kept for the step), 2: a later one
+    pib_weight * qkv = nullptr;                       // rows: W_q (heads*dim) | W_k (kv_heads*dim) | W_v (kv_heads*vdim); delta rule: ... | W_g (heads*vdim) | W_b (heads) | W_a (heads)
+    float * conv = nullptr;                           // [channels of q | k | v][taps]
+    float * q_norm = nullptr, * k_norm = nullptr;     // [dim], shared by the heads
+    float   lambda = 0.f;                             // v <- (1 - lambda) v + lambda v_first
+    // ---- RWKV-style time mixing (PIB_MIXER_WKV) ----
+    float * mu = nullptr;                             // [5][width]: r, k, v, g, w
+    pib_weight * rkvg = nullptr;                      // 4 problems [heads*dim][width]: r, k, v, g
+    pib_weight * w1 = nullptr, * w2 = nullptr;        // decay: W_w2 tanh(W_w1 .)
+    int   w_rank = 0;
+    float * w0 = nullptr, * bonus = nullptr;          // [heads*dim] each
+    size_t  shift_off = 0;                            // floats into a slot's state: the previous token's mixer input [width]
+    // ---- gated delta rule (PIB_MIXER_DELTA) ----
+    float * a_log = nullptr, * dt_bias = nullptr;     // [heads]
     // ---- feed-forward ----
     int   ff = 0;
     pib_weight * up = nullptr, * down = nullptr;
@@ -44,12 +70,17 @@ struct pib_hlayer {
     pib_weight * e_up = nullptr, * e_down = nullptr;  // experts stacked: [E * ff_e][width], [E * width][ff_e]
     pib_weight * router = nullptr;                    // always float32
     pib_weight * s_up = nullptr, * s_down = nullptr;
+    int   route = PIB_ROUTE_SOFTMAX_RENORM, expert = PIB_EXPERT_RELU2;
+    float limit_e = 0.f, limit_s = 0.f;               // clamped gated experts: e_up / s_up hold rows gate | up (s_up one more row: the shared expert's gate logit)
+    int   s_gate = 0;
 };
 
 struct pib_hybrid {
     int     dtype = PIB_TYPE_BF16;                    // PIB_TYPE_BF16: matmul operands rounded to bfloat16, fp32 accumulation; PIB_TYPE_F32: all fp32
+    int     form = PIB_FORM_POSTNORM;
     int     taps = 1;
     float   eps = 1e-5f;
+    float   embd_scale = 1.f, logit_scale = 1.f;      // parallel form: x = embedding * embd_scale, logits = head(norm(x)) * logit_scale
     float * embd_norm = nullptr;
     std::vector<pib_hlayer> layers;
     size_t  state_floats = 0;                         // per state slot
@@ -59,6 +90,7 @@ struct pib_hybrid {
     std::vector<Rope> ropes;
     // widest per-token scratch rows over all layers
     int     w_proj = 0, w_cq = 0, w_q = 0, w_lat = 0, w_att = 0, w_pairs = 0, w_eup = 0, w_router = 0;
+    int     w_conv = 0, w_vfirst = 0, w_shift = 0;    // convolved q | k | v rows, the first mixing layer's values, the five token-shift mixes
 };
 
 struct pib_hybrid_ctx;
@@ -103,17 +135,38 @@ int pib_embed_ln(const pib_weight * embd, const int32_t * tok, const float * w, 
 int pib_layer_norm(const float * in, const float * w, float eps, int T, int W, float * out, int accumulate, cudaStream_t st);
 int pib_canon_conv(const float * x, const float * w, int taps, const pib_hbatch & b, float * state, size_t state_stride, size_t tail_off, int W, float * h,
                    cudaStream_t st);
+int pib_chan_conv(const float * u, int ldu, const float * w, int taps, const pib_hbatch & b, float * state, size_t state_stride, size_t tail_off, int C, float * out, int ldo,
+                  int add_input, int silu, cudaStream_t st);
 int pib_latent_prep(const float * proj, int ldp, const pib_hlayer & L, const float * dq_norm, const float * dkv_norm, float eps, const pib_hbatch & b,
                     const float2 * rope, int rope_n_pos, float * cq, float * cache, int cache_row, cudaStream_t st);
 int pib_latent_attention(const float * q, const float * qlat, const pib_hlayer & L, const pib_hbatch & b, const float2 * rope, int rope_n_pos,
                          const float * cache, int cache_row, const int32_t * cellmap, int n_ctx, float * ctx, const int32_t * skip, cudaStream_t st);
 int pib_latent_attention_mm(const float * q, const float * qlat, const pib_hlayer & L, const pib_hbatch & b, const float2 * rope, const float * cache, int cache_row,
                             const int32_t * map, int t0, int nq, int j0, int NK, void * Kb, void * Vt, float * Qc, float * S, void * P, float * ctx, cudaStream_t st);
+int pib_window_softmax(float * S, void * P, int NKp, int NK, int j0, int window, const int32_t * pos, int t0, int n_rows, int rows_per_z, int rep, const float * sink,
+                       cudaStream_t st);
 int pib_hgrn2_gates(float * qfv, int ld, const float * f_bias, const float * lower, int T, int HD, cudaStream_t st);
 int pib_hgrn2_scan(const float * qfv, int ld, const pib_hlayer & L, const pib_hbatch & b, float * state, size_t state_stride, const float * onorm, float eps,
                    float * out, cudaStream_t st);
 int pib_polynorm(float * z, int T, int F, const float * act4, float eps, cudaStream_t st);
-int pib_moe_route(const float * logits, int T, int E, int top, int32_t * ids, float * wts, cudaStream_t st);
+int pib_moe_route(const float * logits, int T, int E, int top, int mode, int32_t * ids, float * wts, cudaStream_t st);
 int pib_moe_sort(const int32_t * ids, int n_pairs, int E, int32_t * counts, int32_t * offs, int32_t * perm, int32_t * inv, cudaStream_t st);
 int pib_moe_combine(const float * shared, const float * edn, const float * wts, const int32_t * inv, int T, int top, int W, float * y, cudaStream_t st);
 int pib_cellmap_set(int32_t * cellmap, int n_ctx, const pib_hbatch & b, cudaStream_t st);
+
+// mixer_kernels.cu
+int pib_embed_scale(const pib_weight * embd, const int32_t * tok, float scale, int T, int W, float * x, cudaStream_t st);
+int pib_rms_norm2(const float * x, const float * w1, const float * w2, float eps, float out_scale, int T, int W, float * h1, float * h2, cudaStream_t st);
+int pib_swa_prep(const float * cv, int ldc, const pib_hlayer & L, float eps, const pib_hbatch & b, float * q, float * cache, int cache_row, float * vfirst, cudaStream_t st);
+int pib_kv_attention(const float * q, const pib_hlayer & L, const pib_hbatch & b, const float * cache, int cache_row, const int32_t * cellmap, int n_ctx, float * out,
+                     const int32_t * skip, cudaStream_t st);
+int pib_kv_attention_mm(const float * q, const pib_hlayer & L, const pib_hbatch & b, const float * cache, int cache_row, const int32_t * map, int t0, int nq, int j0, int NK,
+                        void * Kb, void * Vt, float * Qc, float * S, void * P, float * out, cudaStream_t st);
+int pib_token_shift(const float * h, const float * mu, int n_mix, const pib_hbatch & b, float * state, size_t state_stride, size_t shift_off, int W, float * mixes, cudaStream_t st);
+int pib_rows_act(float * z, int ld, int n, int T, int op, const float * bias, cudaStream_t st);           // op 0: tanh; 1: exp(-exp(z + bias))
+int pib_delta_prep(float * cv, int ldc, const pib_hlayer & L, const float * proj, int ldp, int b_off, int a_off, float * bg, int T, cudaStream_t st);
+int pib_wkv_scan(const float * rkvg, int ld, const float * wdec, int ldw, const pib_hlayer & L, const pib_hbatch & b, float * state, size_t state_stride, float * out, cudaStream_t st);
+int pib_delta_scan(const float * cv, int ldc, const float * bg, const pib_hlayer & L, const pib_hbatch & b, float * state, size_t state_stride, float * out, cudaStream_t st);
+int pib_gated_head_norm(float * o, int T, int H, int V, const float * w, int w_hs, const float * gate, int ldg, float eps, cudaStream_t st);
+int pib_glu_clamp(float * gu, int ld, int F, float limit, const float * scale, const int32_t * scale_of, int n_rows, cudaStream_t st);
+int pib_parallel_sum(float * x, const float * mixer, const float * shared, const float * sgl, int ldsg, const float * edn, const int32_t * inv, int top, int T, int W, cudaStream_t st);

@@ -79,28 +79,31 @@ int pib_layer_norm(const float * in, const float * w, float eps, int T, int W, f
 }
 
 // ---- causal convolution with a per-sequence tail ---------------------------------------------------------------------------------
-// h[t] = x[t] + sum_j w[:, j] * in(t - taps + 1 + j); in() is this batch's x inside the token's segment, the slot's tail before it
+// out[t][c] = (flags & 1 ? u[t][c] : 0) + sum_j w[c][j] * in(t - taps + 1 + j)[c], then silu if flags & 2; in() is this batch's u inside the
+// token's segment, the slot's tail ([taps-1][C]) before it.  u rows have pitch ldu, out rows pitch ldo; C channels.
 #define CANON_MAX_TAPS 16
-__global__ void __launch_bounds__(256) canon_kernel(const float * __restrict__ x, const float * __restrict__ w, int taps, const int32_t * __restrict__ seg,
+enum { CONV_ADD_INPUT = 1, CONV_SILU = 2 };
+__global__ void __launch_bounds__(256) canon_kernel(const float * __restrict__ x, int ldu, const float * __restrict__ w, int taps, const int32_t * __restrict__ seg,
                                                     const int32_t * __restrict__ seg_start, const int32_t * __restrict__ seg_slot,
-                                                    const float * __restrict__ state, size_t state_stride, size_t tail_off, int W, float * __restrict__ h) {
+                                                    const float * __restrict__ state, size_t state_stride, size_t tail_off, int W, float * __restrict__ h, int ldo, int flags) {
     pib_pdl_wait();
     pib_pdl_trigger();
     const int t = blockIdx.x, sg = seg[t], s0 = seg_start[sg];
     const float * tail = state + (size_t) seg_slot[sg] * state_stride + tail_off;
     for (int c = threadIdx.x; c < W; c += blockDim.x) {
-        float acc = x[(size_t) t * W + c];
+        float acc = (flags & CONV_ADD_INPUT) ? x[(size_t) t * ldu + c] : 0.f;
         for (int j = 0; j < taps; j++) {
             const int tau = t - (taps - 1) + j;
-            const float v = tau >= s0 ? x[(size_t) tau * W + c] : tail[(size_t) (taps - 1 + tau - s0) * W + c];
+            const float v = tau >= s0 ? x[(size_t) tau * ldu + c] : tail[(size_t) (taps - 1 + tau - s0) * W + c];
             acc = fmaf(w[(size_t) c * taps + j], v, acc);
         }
-        h[(size_t) t * W + c] = acc;
+        if (flags & CONV_SILU) acc = acc / (1.0f + expf(-acc));
+        h[(size_t) t * ldo + c] = acc;
     }
 }
 
 // after canon_kernel: the last taps-1 inputs of every segment become its slot's tail (old tail rows move up when the segment is shorter)
-__global__ void __launch_bounds__(256) canon_tail_kernel(const float * __restrict__ x, int taps, const int32_t * __restrict__ seg_start, const int32_t * __restrict__ seg_len,
+__global__ void __launch_bounds__(256) canon_tail_kernel(const float * __restrict__ x, int ldu, int taps, const int32_t * __restrict__ seg_start, const int32_t * __restrict__ seg_len,
                                                          const int32_t * __restrict__ seg_slot, float * __restrict__ state, size_t state_stride, size_t tail_off, int W) {
     pib_pdl_wait();
     pib_pdl_trigger();
@@ -112,7 +115,7 @@ __global__ void __launch_bounds__(256) canon_tail_kernel(const float * __restric
         for (int k = 0; k < CANON_MAX_TAPS; k++) {
             if (k < taps - 1) {
                 const int tau = s1 - (taps - 1) + k;
-                v[k] = tau >= s0 ? x[(size_t) tau * W + c] : tail[(size_t) (taps - 1 + tau - s0) * W + c];
+                v[k] = tau >= s0 ? x[(size_t) tau * ldu + c] : tail[(size_t) (taps - 1 + tau - s0) * W + c];
             }
         }
 #pragma unroll
@@ -120,13 +123,20 @@ __global__ void __launch_bounds__(256) canon_tail_kernel(const float * __restric
     }
 }
 
+// the general form: C channels of rows u (pitch ldu) -> out (pitch ldo); add_input: out += u; silu: activation on the way out
+int pib_chan_conv(const float * u, int ldu, const float * w, int taps, const pib_hbatch & b, float * state, size_t state_stride, size_t tail_off, int C, float * out, int ldo,
+                  int add_input, int silu, cudaStream_t st) {
+    if (taps > CANON_MAX_TAPS || taps < 1) { pib_set_error("convolution: %d taps (1 to %d)", taps, CANON_MAX_TAPS); return PIB_ERR_UNSUPP; }
+    const int flags = (add_input ? CONV_ADD_INPUT : 0) | (silu ? CONV_SILU : 0);
+    pib_launch(canon_kernel, dim3(b.T), dim3(256), (size_t) (0), st, u, ldu, w, taps, b.seg, b.seg_start, b.seg_slot, (const float *) state, state_stride, tail_off, C, out, ldo, flags);
+    CKL();
+    if (taps > 1) { pib_launch(canon_tail_kernel, dim3(b.S), dim3(256), (size_t) (0), st, u, ldu, taps, b.seg_start, b.seg_len, b.seg_slot, state, state_stride, tail_off, C); CKL(); }
+    return PIB_OK;
+}
+// h = x + conv(x) over the model's width, in front of a mixer
 int pib_canon_conv(const float * x, const float * w, int taps, const pib_hbatch & b, float * state, size_t state_stride, size_t tail_off, int W, float * h,
                    cudaStream_t st) {
-    if (taps > CANON_MAX_TAPS) { pib_set_error("convolution: %d taps (max %d)", taps, CANON_MAX_TAPS); return PIB_ERR_UNSUPP; }
-    pib_launch(canon_kernel, dim3(b.T), dim3(256), (size_t) (0), st, x, w, taps, b.seg, b.seg_start, b.seg_slot, state, state_stride, tail_off, W, h);
-    CKL();
-    if (taps > 1) { pib_launch(canon_tail_kernel, dim3(b.S), dim3(256), (size_t) (0), st, x, taps, b.seg_start, b.seg_len, b.seg_slot, state, state_stride, tail_off, W); CKL(); }
-    return PIB_OK;
+    return pib_chan_conv(x, W, w, taps, b, state, state_stride, tail_off, W, h, W, 1, 0, st);
 }
 
 // ---- position -> cell table of each state slot -----------------------------------------------------------------------------------
@@ -334,17 +344,19 @@ __global__ void __launch_bounds__(128) lat_qcat_kernel(const float * __restrict_
         out[R + i] = v * scale;
     }
 }
-// one score row per (token, head), in place: keys outside [p - window + 1, p] and the pad get weight 0, the sink one share of the denominator
+// one score row per (token, head), in place: keys outside [p - window + 1, p] and the pad get weight 0, the sink (optional) one share of
+// the denominator.  Rows come in groups of rows_per_z (one group per problem of the score matmul), inside a group `rep` heads per token:
+// token t0 + (row % rows_per_z) / rep, head (row / rows_per_z) * rep + (row % rows_per_z) % rep.
 __global__ void __launch_bounds__(256) lat_softmax_kernel(float * __restrict__ S, __nv_bfloat16 * __restrict__ P, int NKp, int NK, int j0, int window,
-                                                          const int32_t * __restrict__ pos, int t0, int H, const float * __restrict__ sink) {
+                                                          const int32_t * __restrict__ pos, int t0, int rows_per_z, int rep, const float * __restrict__ sink) {
     pib_pdl_wait();
     pib_pdl_trigger();
     __shared__ float red[32];
-    const int row = blockIdx.x, t = t0 + row / H, h = row % H, p = pos[t];
+    const int row = blockIdx.x, rz = row % rows_per_z, t = t0 + rz / rep, h = (row / rows_per_z) * rep + rz % rep, p = pos[t];
     float *   s = S + (size_t) row * NKp;
     __nv_bfloat16 * pw = P + (size_t) row * 2 * NKp;   // [weights' bfloat16 part | what the rounding left]: the value matmul sees both, so the weights keep fp32 accuracy
     const int lo = max(0, p - window + 1) - j0, hi = p - j0;            // valid columns [lo, hi]
-    const float sk = sink[h];
+    const float sk = sink ? sink[h] : -INFINITY;
     float m = sk;
     for (int j = lo + (int) threadIdx.x; j <= hi; j += blockDim.x) m = fmaxf(m, s[j]);
     m = warp_max(m);
@@ -358,7 +370,7 @@ __global__ void __launch_bounds__(256) lat_softmax_kernel(float * __restrict__ S
         s[j] = e;
         sum += e;
     }
-    const float inv = 1.0f / (block_sum(sum, red) + expf(sk - m));
+    const float inv = 1.0f / (block_sum(sum, red) + (sink ? expf(sk - m) : 0.f));
     for (int j = threadIdx.x; j < NKp; j += blockDim.x) {
         const float p = s[j] * inv;
         const __nv_bfloat16 hi16 = __float2bfloat16_rn(p);
@@ -366,6 +378,12 @@ __global__ void __launch_bounds__(256) lat_softmax_kernel(float * __restrict__ S
         pw[NKp + j] = __float2bfloat16_rn(p - __bfloat162float(hi16));
     }
     (void) NK; (void) hi;
+}
+int pib_window_softmax(float * S, void * P, int NKp, int NK, int j0, int window, const int32_t * pos, int t0, int n_rows, int rows_per_z, int rep, const float * sink,
+                       cudaStream_t st) {
+    pib_launch(lat_softmax_kernel, dim3(n_rows), dim3(256), (size_t) (0), st, S, (__nv_bfloat16 *) P, NKp, NK, j0, window, pos, t0, rows_per_z, rep, sink);
+    CKL();
+    return PIB_OK;
 }
 
 // bfloat16 weight rows back to fp32 rows (same pitch), for the few-row matmul kernels
@@ -389,8 +407,7 @@ int pib_latent_attention_mm(const float * q, const float * qlat, const pib_hlaye
     a.W = Kb; a.wtype = PIB_TYPE_BF16; a.ldw = RK; a.X = Qc; a.ldx = RK; a.Y = S; a.ldy = NKp; a.M = nq * H; a.N = NK; a.K = RK;
     int rc = pib_dense_mm(a, st);
     if (rc != PIB_OK) return rc;
-    pib_launch(lat_softmax_kernel, dim3(nq * H), dim3(256), (size_t) (0), st, S, (__nv_bfloat16 *) P, NKp, NK, j0, L.window, b.pos, t0, H, L.sink);
-    CKL();
+    if ((rc = pib_window_softmax(S, P, NKp, NK, j0, L.window, b.pos, t0, nq * H, nq * H, H, L.sink, st)) != PIB_OK) return rc;
     pib_mm v;
     v.W = Vt; v.wtype = PIB_TYPE_BF16; v.ldw = 2 * NKp; v.Y = ctx + (size_t) t0 * H * R; v.ldy = R; v.M = nq * H; v.N = R; v.K = 2 * NKp;
     if (nq * H > 16) { v.X = (const float *) P; v.ldx = 2 * NKp; v.x_bf16 = 1; return pib_dense_mm(v, st); }
@@ -545,9 +562,11 @@ int pib_polynorm(float * z, int T, int F, const float * act4, float eps, cudaStr
 }
 
 // ---- mixture of experts ------------------------------------------------------------------------------------------------------------
-// one warp per token: softmax over the E router logits, the `top` largest scores (ties: the lower index), weights = score / (sum of the chosen + 1e-20)
+// one warp per token: the `top` largest logits (ties: the lower index).  mode PIB_ROUTE_SOFTMAX_RENORM: scores = softmax over the E
+// logits, weights = score / (sum of the chosen + 1e-20); PIB_ROUTE_SIGMOID: weights = sigmoid(logit) of the chosen, as they are (the
+// order of the logits is the order of their sigmoids)
 #define MOE_MAX_TOP 16
-__global__ void moe_route_kernel(const float * __restrict__ logits, int T, int E, int top, int32_t * __restrict__ ids, float * __restrict__ wts) {
+__global__ void moe_route_kernel(const float * __restrict__ logits, int T, int E, int top, int mode, int32_t * __restrict__ ids, float * __restrict__ wts) {
     pib_pdl_wait();
     pib_pdl_trigger();
     const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
@@ -576,15 +595,15 @@ __global__ void moe_route_kernel(const float * __restrict__ logits, int T, int E
             if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
         }
         chosen[k] = bi;
-        score[k]  = expf(bv - mx) / sum;
+        score[k]  = mode == PIB_ROUTE_SIGMOID ? 1.0f / (1.0f + expf(-bv)) : expf(bv - mx) / sum;
         tot += score[k];
     }
     if (lane == 0)
-        for (int k = 0; k < top; k++) { ids[(size_t) t * top + k] = chosen[k]; wts[(size_t) t * top + k] = score[k] / (tot + 1e-20f); }
+        for (int k = 0; k < top; k++) { ids[(size_t) t * top + k] = chosen[k]; wts[(size_t) t * top + k] = mode == PIB_ROUTE_SIGMOID ? score[k] : score[k] / (tot + 1e-20f); }
 }
-int pib_moe_route(const float * logits, int T, int E, int top, int32_t * ids, float * wts, cudaStream_t st) {
+int pib_moe_route(const float * logits, int T, int E, int top, int mode, int32_t * ids, float * wts, cudaStream_t st) {
     if (top > MOE_MAX_TOP || top > E) { pib_set_error("router: top %d of %d experts (max %d)", top, E, MOE_MAX_TOP); return PIB_ERR_UNSUPP; }
-    pib_launch(moe_route_kernel, dim3((T + 7) / 8), dim3(256), (size_t) (0), st, logits, T, E, top, ids, wts);
+    pib_launch(moe_route_kernel, dim3((T + 7) / 8), dim3(256), (size_t) (0), st, logits, T, E, top, mode, ids, wts);
     CKL();
     return PIB_OK;
 }

@@ -1,0 +1,544 @@
+// mixer_kernels.cu -- more parts for layer-list models (hybrid.cuh), all fp32:
+//
+//   embedding rows times a constant; RMS norm with a weight stored around zero, two norms of the same row in one pass
+//   windowed softmax attention over cached key / value heads: per-head RMS norm of queries and keys, value mixing with the values an
+//       earlier layer computed for the same token, grouped queries, an optional sink logit
+//   RWKV-style time mixing: the five token-shift mixes, the per-channel decay, and the recurrence
+//       o_t = (S + diag(u) k_t v_t^T)^T r_t,  S <- diag(w_t) S + k_t v_t^T
+//   the gated delta rule: S <- g_t S,  e_t = beta_t (v_t - S^T k_t),  S <- S + k_t e_t^T,  o_t = S^T q_t
+//   RMS norm of each head's output times a weight times silu(gate)
+//   clamped gated experts: y = a sigmoid(1.702 a) (b + 1), a = min(gate, limit), b = clamp(up, -limit, limit)
+//   the parallel layer's sum: x += mixer + shared expert * sigmoid(gate logit) + routed experts
+#include "hybrid.cuh"
+
+#include <cuda_bf16.h>
+
+#define CKL() do { cudaError_t e__ = cudaGetLastError(); if (e__ != cudaSuccess) { pib_set_error("%s:%d: launch failed: %s", __FILE__, __LINE__, cudaGetErrorString(e__)); return PIB_ERR_CUDA; } } while (0)
+
+__device__ __forceinline__ float mk_block_sum(float v, float * red) {
+    v = warp_sum(v);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = 0.f;
+    for (int i = 0; i < nw; i++) t += red[i];
+    return t;
+}
+__device__ __forceinline__ float mk_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float mk_silu(float z) { return z / (1.0f + expf(-z)); }
+
+// ---- embedding, norms ------------------------------------------------------------------------------------------------------------
+template <typename WT>
+__global__ void __launch_bounds__(256) embed_scale_kernel(const WT * __restrict__ embd, const int32_t * __restrict__ tok, float scale, int W, float * __restrict__ x) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
+    const WT * r = embd + (size_t) tok[blockIdx.x] * W;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) x[(size_t) blockIdx.x * W + i] = (float) r[i] * scale;
+}
+int pib_embed_scale(const pib_weight * embd, const int32_t * tok, float scale, int T, int W, float * x, cudaStream_t st) {
+    if (embd->type == PIB_TYPE_BF16) pib_launch(embed_scale_kernel<__nv_bfloat16>, dim3(T), dim3(256), (size_t) 0, st, (const __nv_bfloat16 *) embd->base, tok, scale, W, x);
+    else                             pib_launch(embed_scale_kernel<float>, dim3(T), dim3(256), (size_t) 0, st, (const float *) embd->base, tok, scale, W, x);
+    CKL();
+    return PIB_OK;
+}
+
+// h1 = x / sqrt(mean(x^2) + eps) * (1 + w1) * out_scale, and (w2 != null) h2 the same with w2: both norms of a parallel layer read x once
+__global__ void __launch_bounds__(256) rms_norm2_kernel(const float * __restrict__ x, const float * __restrict__ w1, const float * __restrict__ w2, float eps, float out_scale,
+                                                        int W, float * __restrict__ h1, float * __restrict__ h2) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
+    extern __shared__ float srow[];
+    __shared__ float red[32];
+    const float * r = x + (size_t) blockIdx.x * W;
+    float s = 0.f;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) { const float v = r[i]; srow[i] = v; s = fmaf(v, v, s); }
+    const float inv = out_scale / sqrtf(mk_block_sum(s, red) / W + eps);
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        const float v = srow[i] * inv;
+        h1[(size_t) blockIdx.x * W + i] = v * (1.0f + w1[i]);
+        if (w2) h2[(size_t) blockIdx.x * W + i] = v * (1.0f + w2[i]);
+    }
+}
+int pib_rms_norm2(const float * x, const float * w1, const float * w2, float eps, float out_scale, int T, int W, float * h1, float * h2, cudaStream_t st) {
+    pib_launch(rms_norm2_kernel, dim3(T), dim3(256), (size_t) W * 4, st, x, w1, w2, eps, out_scale, W, h1, h2);
+    CKL();
+    return PIB_OK;
+}
+
+// ---- windowed attention: what follows the convolution ------------------------------------------------------------------------------
+// cv[t] = [q (H*D) | k (G*D) | v (G*V)] after the convolution.  q[t][h] = RMS(q_h) * q_norm; the token's cell gets
+// [RMS(k_g) * k_norm (G*D) | v' (G*V)], v' = v, or (1 - lambda) v + lambda v_first for a later mixing layer; the first mixing layer
+// leaves its v in vfirst.  One warp per head (query heads, then key heads), the block's threads over the values.
+__global__ void __launch_bounds__(256) swa_prep_kernel(const float * __restrict__ cv, int ldc, int H, int G, int D, int V, const float * __restrict__ q_norm,
+                                                       const float * __restrict__ k_norm, float eps, int v_mix, float lambda, const int32_t * __restrict__ cell,
+                                                       float * __restrict__ q, float * __restrict__ cache, int cache_row, float * __restrict__ vfirst) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const float * r = cv + (size_t) t * ldc;
+    float * row = cache + (size_t) cell[t] * cache_row;
+    for (int hh = warp; hh < H + G; hh += nw) {
+        const float * src = r + (size_t) hh * D;
+        const float * w = hh < H ? q_norm : k_norm;
+        float * dst = hh < H ? q + ((size_t) t * H + hh) * D : row + (size_t) (hh - H) * D;
+        float s = 0.f;
+        for (int i = lane; i < D; i += 32) s = fmaf(src[i], src[i], s);
+        const float inv = 1.0f / sqrtf(warp_sum(s) / D + eps);
+        for (int i = lane; i < D; i += 32) dst[i] = src[i] * inv * w[i];
+    }
+    const float * v = r + (size_t) (H + G) * D;
+    for (int i = threadIdx.x; i < G * V; i += blockDim.x) {
+        float x = v[i];
+        if (v_mix == 1) vfirst[(size_t) t * G * V + i] = x;
+        else if (v_mix == 2) x = (1.0f - lambda) * x + lambda * vfirst[(size_t) t * G * V + i];
+        row[(size_t) G * D + i] = x;
+    }
+}
+int pib_swa_prep(const float * cv, int ldc, const pib_hlayer & L, float eps, const pib_hbatch & b, float * q, float * cache, int cache_row, float * vfirst, cudaStream_t st) {
+    pib_launch(swa_prep_kernel, dim3(b.T), dim3(256), (size_t) 0, st, cv, ldc, L.heads, L.kv_heads, L.dim, L.vdim, L.q_norm, L.k_norm, eps, L.v_mix, L.lambda, b.cell, q, cache,
+               cache_row, vfirst);
+    CKL();
+    return PIB_OK;
+}
+
+// grid (token, head group); a block holds HPB query heads x KS key shares, one warp each.  A warp walks its share of the window
+// [max(0, p - window + 1), p] through the slot's position -> cell table, keeps a running maximum / denominator / weighted sum of value
+// rows, and the shares of a head are merged in shared memory.  A sink (optional) is one more logit without a row: the running state of
+// share 0 starts at (max = sink, denominator = 1).
+template <int RPL>
+__global__ void __launch_bounds__(512) kv_attn_kernel(const float * __restrict__ q, int H, int G, int D, int V, float scale, int window, const float * __restrict__ sink,
+                                                      const int32_t * __restrict__ pos, const int32_t * __restrict__ slot, const float * __restrict__ cache, int cache_row,
+                                                      const int32_t * __restrict__ cellmap, int n_ctx, int HPB, int KS, float * __restrict__ out,
+                                                      const int32_t * __restrict__ skip) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
+    extern __shared__ float sm[];                 // [HPB * KS][V + 2] partial states
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (skip && skip[t]) return;                  // this token's segment goes through the matmul form
+    const int hl = warp / KS, ks = warp % KS, h = blockIdx.y * HPB + hl;
+    const int p = pos[t], lo = max(0, p - window + 1);
+    const bool live = h < H;
+    float qv[RPL], acc[RPL];
+    float m = -INFINITY, l = 0.f;
+    if (live) {
+        const int g = h / (H / G);
+        const float * qp = q + ((size_t) t * H + h) * D;
+#pragma unroll
+        for (int i = 0; i < RPL; i++) { const int r = i * 32 + lane; qv[i] = r < D ? qp[r] * scale : 0.f; acc[i] = 0.f; }
+        if (ks == 0 && sink) { m = sink[h]; l = 1.f; }
+        const int32_t * map = cellmap + (size_t) slot[t] * n_ctx;
+        const size_t ko = (size_t) g * D, vo = (size_t) G * D + (size_t) g * V;
+        for (int j = lo + ks; j <= p; j += KS) {
+            const float * row = cache + (size_t) map[j] * cache_row;
+            float s = 0.f, c[RPL];
+#pragma unroll
+            for (int i = 0; i < RPL; i++) { const int r = i * 32 + lane; if (r < D) s = fmaf(qv[i], row[ko + r], s); c[i] = r < V ? row[vo + r] : 0.f; }
+            s = warp_sum(s);
+            const float mn = fmaxf(m, s), a = expf(m - mn), e = expf(s - mn);         // m == -inf only before the first key: a = 0
+            l = l * a + e;
+#pragma unroll
+            for (int i = 0; i < RPL; i++) acc[i] = fmaf(acc[i], a, e * c[i]);
+            m = mn;
+        }
+        float * part = sm + (size_t) warp * (V + 2);
+#pragma unroll
+        for (int i = 0; i < RPL; i++) { const int r = i * 32 + lane; if (r < V) part[r] = acc[i]; }
+        if (lane == 0) { part[V] = m; part[V + 1] = l; }
+    }
+    __syncthreads();
+    if (live && ks == 0) {
+        const float * base = sm + (size_t) (hl * KS) * (V + 2);
+        float M = -INFINITY;
+        for (int k = 0; k < KS; k++) M = fmaxf(M, base[(size_t) k * (V + 2) + V]);
+        float Lsum = 0.f, o[RPL];
+#pragma unroll
+        for (int i = 0; i < RPL; i++) o[i] = 0.f;
+        for (int k = 0; k < KS; k++) {
+            const float * pk = base + (size_t) k * (V + 2);
+            const float   mk = pk[V];
+            if (mk == -INFINITY) continue;           // a share that saw no key
+            const float f = expf(mk - M);
+            Lsum = fmaf(pk[V + 1], f, Lsum);
+#pragma unroll
+            for (int i = 0; i < RPL; i++) { const int r = i * 32 + lane; if (r < V) o[i] = fmaf(pk[r], f, o[i]); }
+        }
+        const float inv = 1.0f / Lsum;
+        float * op = out + ((size_t) t * H + h) * V;
+#pragma unroll
+        for (int i = 0; i < RPL; i++) { const int r = i * 32 + lane; if (r < V) op[r] = o[i] * inv; }
+    }
+}
+
+int pib_kv_attention(const float * q, const pib_hlayer & L, const pib_hbatch & b, const float * cache, int cache_row, const int32_t * cellmap, int n_ctx, float * out,
+                     const int32_t * skip, cudaStream_t st) {
+    const int H = L.heads, V = L.vdim, R = L.dim > L.vdim ? L.dim : L.vdim;
+    const int HPB = (long long) b.T * H <= 1024 ? 1 : (H < 4 ? H : 4);
+    int KS = 16 / HPB;
+    if (L.window < 64) KS = 1;
+    const size_t smem = (size_t) HPB * KS * (V + 2) * 4;
+    dim3 grid((unsigned) b.T, (unsigned) ((H + HPB - 1) / HPB));
+    const int threads = HPB * KS * 32;
+#define KA_GO(RPL) do {                                                                                                              \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kv_attn_kernel<RPL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem);   \
+        pib_launch(kv_attn_kernel<RPL>, dim3(grid), dim3(threads), (size_t) smem, st, q, H, L.kv_heads, L.dim, V, L.scale, L.window, (const float *) L.sink, b.pos, b.slot, cache, \
+                   cache_row, cellmap, n_ctx, HPB, KS, out, skip);                                                                  \
+    } while (0)
+    if (R <= 32) KA_GO(1); else if (R <= 64) KA_GO(2); else if (R <= 128) KA_GO(4); else if (R <= 256) KA_GO(8); else if (R <= 512) KA_GO(16);
+    else { pib_set_error("attention: head size %d (max 512)", R); return PIB_ERR_UNSUPP; }
+#undef KA_GO
+    CKL();
+    return PIB_OK;
+}
+
+// ---- the same attention as matmuls (long portions, served mode) -----------------------------------------------------------------------
+// For a block of nq consecutive tokens of one segment and the keys [j0, j0 + NK) it can see, one problem per key / value head g:
+// scores [nq * rep][NK] = (scale * queries of the rep heads that share g) x keys^T, the masked softmax over each row, outputs = weights x
+// values.  These kernels prepare the operands -- keys as bfloat16 [G][NKp][D], values transposed and twice side by side [G][V][2 NKp]
+// (a weight enters the value matmul as its bfloat16 part plus the remainder of that rounding), query rows [G][nq * rep][D] -- and put the
+// outputs [G][nq * rep][V] back in token order.
+__global__ void __launch_bounds__(128) kv_gather_kernel(const float * __restrict__ cache, int cache_row, const int32_t * __restrict__ map, int j0, int NK, int NKp, int G, int D,
+                                                        int V, __nv_bfloat16 * __restrict__ Kb, __nv_bfloat16 * __restrict__ Vt) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
+    const int j = blockIdx.x;
+    if (j < NK) {
+        const float * row = cache + (size_t) map[j0 + j] * cache_row;
+        for (int i = threadIdx.x; i < G * D; i += blockDim.x) Kb[((size_t) (i / D) * NKp + j) * D + i % D] = __float2bfloat16_rn(row[i]);
+        for (int i = threadIdx.x; i < G * V; i += blockDim.x) {
+            const __nv_bfloat16 v = __float2bfloat16_rn(row[(size_t) G * D + i]);
+            Vt[(size_t) i * 2 * NKp + j] = v; Vt[(size_t) i * 2 * NKp + NKp + j] = v;
+        }
+    } else {
+        for (int i = threadIdx.x; i < G * D; i += blockDim.x) Kb[((size_t) (i / D) * NKp + j) * D + i % D] = __float2bfloat16_rn(0.f);
+        for (int i = threadIdx.x; i < G * V; i += blockDim.x) { Vt[(size_t) i * 2 * NKp + j] = __float2bfloat16_rn(0.f); Vt[(size_t) i * 2 * NKp + NKp + j] = __float2bfloat16_rn(0.f); }
+    }
+}
+// dir 0: Qc[g][ti * rep + hr][D] = scale * q[t0 + ti][g * rep + hr][D];   dir 1: out[t0 + ti][g * rep + hr][V] = O[g][ti * rep + hr][V]
+__global__ void __launch_bounds__(128) kv_regroup_kernel(const float * __restrict__ src, float * __restrict__ dst, int H, int rep, int nq, int n, int t0, float scale, int dir) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
+    const int ti = blockIdx.x, h = blockIdx.y, g = h / rep, hr = h % rep;
+    const size_t tok = ((size_t) (t0 + ti) * H + h) * n, grp = ((size_t) g * nq * rep + (size_t) ti * rep + hr) * n;
+    if (dir == 0) for (int i = threadIdx.x; i < n; i += blockDim.x) dst[grp + i] = src[tok + i] * scale;
+    else          for (int i = threadIdx.x; i < n; i += blockDim.x) dst[tok + i] = src[grp + i];
+}
+int pib_kv_attention_mm(const float * q, const pib_hlayer & L, const pib_hbatch & b, const float * cache, int cache_row, const int32_t * map, int t0, int nq, int j0, int NK,
+                        void * Kb, void * Vt, float * Qc, float * S, void * P, float * out, cudaStream_t st) {
+    const int H = L.heads, G = L.kv_heads, D = L.dim, V = L.vdim, rep = H / G, NKp = (NK + 7) & ~7, M = nq * rep;
+    pib_launch(kv_gather_kernel, dim3(NKp), dim3(128), (size_t) 0, st, cache, cache_row, map, j0, NK, NKp, G, D, V, (__nv_bfloat16 *) Kb, (__nv_bfloat16 *) Vt);
+    CKL();
+    pib_launch(kv_regroup_kernel, dim3((unsigned) nq, (unsigned) H), dim3(128), (size_t) 0, st, q, Qc, H, rep, nq, D, t0, L.scale, 0);
+    CKL();
+    pib_mm a;
+    a.W = Kb; a.wtype = PIB_TYPE_BF16; a.ldw = D; a.wz = (int64_t) NKp * D; a.X = Qc; a.ldx = D; a.xz = (int64_t) M * D; a.Y = S; a.ldy = NKp; a.yz = (int64_t) M * NKp;
+    a.M = M; a.N = NK; a.K = D; a.Z = G;
+    int rc = pib_dense_mm(a, st);
+    if (rc != PIB_OK) return rc;
+    if ((rc = pib_window_softmax(S, P, NKp, NK, j0, L.window, b.pos, t0, G * M, M, rep, L.sink, st)) != PIB_OK) return rc;
+    pib_mm v;
+    v.W = Vt; v.wtype = PIB_TYPE_BF16; v.ldw = 2 * NKp; v.wz = (int64_t) V * 2 * NKp; v.X = (const float *) P; v.ldx = 2 * NKp; v.xz = (int64_t) M * 2 * NKp; v.x_bf16 = 1;
+    v.Y = Qc; v.ldy = V; v.yz = (int64_t) M * V; v.M = M; v.N = V; v.K = 2 * NKp; v.Z = G;               // the query rows are used up: the outputs take their place
+    if ((rc = pib_dense_mm(v, st)) != PIB_OK) return rc;
+    pib_launch(kv_regroup_kernel, dim3((unsigned) nq, (unsigned) H), dim3(128), (size_t) 0, st, (const float *) Qc, out, H, rep, nq, V, t0, 1.0f, 1);
+    CKL();
+    return PIB_OK;
+}
+
+// ---- RWKV-style time mixing -----------------------------------------------------------------------------------------------------
+// mixes[t][s] = h[t] + (h[t - 1] - h[t]) * mu[s], s = 0 .. n_mix - 1; h[t - 1] of a segment's first token is the slot's row (zeros at a
+// sequence's start).  The second kernel leaves each segment's last row in the slot.
+__global__ void __launch_bounds__(256) token_shift_kernel(const float * __restrict__ h, const float * __restrict__ mu, int n_mix, const int32_t * __restrict__ seg,
+                                                          const int32_t * __restrict__ seg_start, const int32_t * __restrict__ seg_slot, const float * __restrict__ state,
+                                                          size_t state_stride, size_t shift_off, int W, float * __restrict__ mixes) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
+    const int t = blockIdx.x, sg = seg[t];
+    const float * prev = t > seg_start[sg] ? h + (size_t) (t - 1) * W : state + (size_t) seg_slot[sg] * state_stride + shift_off;
+    const float * cur = h + (size_t) t * W;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const float a = cur[c], d = prev[c] - a;
+        for (int s = 0; s < n_mix; s++) mixes[((size_t) t * n_mix + s) * W + c] = fmaf(d, mu[(size_t) s * W + c], a);
+    }
+}
+__global__ void __launch_bounds__(256) token_shift_tail_kernel(const float * __restrict__ h, const int32_t * __restrict__ seg_start, const int32_t * __restrict__ seg_len,
+                                                               const int32_t * __restrict__ seg_slot, float * __restrict__ state, size_t state_stride, size_t shift_off, int W) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
+    const int sg = blockIdx.x;
+    const float * last = h + (size_t) (seg_start[sg] + seg_len[sg] - 1) * W;
+    float * dst = state + (size_t) seg_slot[sg] * state_stride + shift_off;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) dst[c] = last[c];
+}
+int pib_token_shift(const float * h, const float * mu, int n_mix, const pib_hbatch & b, float * state, size_t state_stride, size_t shift_off, int W, float * mixes, cudaStream_t st) {
+    pib_launch(token_shift_kernel, dim3(b.T), dim3(256), (size_t) 0, st, h, mu, n_mix, b.seg, b.seg_start, b.seg_slot, (const float *) state, state_stride, shift_off, W, mixes);
+    CKL();
+    pib_launch(token_shift_tail_kernel, dim3(b.S), dim3(256), (size_t) 0, st, h, b.seg_start, b.seg_len, b.seg_slot, state, state_stride, shift_off, W);
+    CKL();
+    return PIB_OK;
+}
+
+// elementwise, in place on rows [T][n] with pitch ld: op 0 tanh(z); op 1 the decay exp(-exp(z + bias[i]))
+__global__ void rows_act_kernel(float * __restrict__ z, int ld, int n, int T, int op, const float * __restrict__ bias) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
+    const int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (int64_t) T * n) return;
+    const int t = (int) (i / n), c = (int) (i % n);
+    float * p = z + (size_t) t * ld + c;
+    *p = op == 0 ? tanhf(*p) : expf(-expf(*p + bias[c]));
+}
+int pib_rows_act(float * z, int ld, int n, int T, int op, const float * bias, cudaStream_t st) {
+    const int64_t tot = (int64_t) T * n;
+    pib_launch(rows_act_kernel, dim3((unsigned) ((tot + 255) / 256)), dim3(256), (size_t) 0, st, z, ld, n, T, op, bias);
+    CKL();
+    return PIB_OK;
+}
+
+// ---- the gated delta rule: what follows the convolution ----------------------------------------------------------------------------
+// cv[t] = [q (G*D) | k (G*D) | v (H*V)] after convolution and silu: q and k become unit vectors per head (x / sqrt(sum x^2 + 1e-6)), q
+// also times D^-1/2.  proj[t] holds the raw gate logits b (H) at b_off and a (H) at a_off: bg[t] = [sigmoid(b) (H) | exp(-exp(a_log) softplus(a + dt_bias)) (H)]
+__global__ void __launch_bounds__(128) delta_prep_kernel(float * __restrict__ cv, int ldc, int G, int D, int H, const float * __restrict__ proj, int ldp, int b_off, int a_off,
+                                                         const float * __restrict__ a_log, const float * __restrict__ dt_bias, float * __restrict__ bg) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    float * r = cv + (size_t) t * ldc;
+    const float qs = 1.0f / sqrtf((float) D);
+    for (int hh = warp; hh < 2 * G; hh += nw) {
+        float * x = r + (size_t) hh * D;
+        float s = 0.f;
+        for (int i = lane; i < D; i += 32) s = fmaf(x[i], x[i], s);
+        const float inv = (hh < G ? qs : 1.0f) / sqrtf(warp_sum(s) + 1e-6f);
+        for (int i = lane; i < D; i += 32) x[i] *= inv;
+    }
+    const float * p = proj + (size_t) t * ldp;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        bg[(size_t) t * 2 * H + i] = mk_sigmoid(p[b_off + i]);
+        const float z = p[a_off + i] + dt_bias[i];
+        const float sp = z > 20.f ? z : log1pf(expf(z));
+        bg[(size_t) t * 2 * H + H + i] = expf(-expf(a_log[i]) * sp);
+    }
+}
+int pib_delta_prep(float * cv, int ldc, const pib_hlayer & L, const float * proj, int ldp, int b_off, int a_off, float * bg, int T, cudaStream_t st) {
+    pib_launch(delta_prep_kernel, dim3(T), dim3(128), (size_t) 0, st, cv, ldc, L.kv_heads, L.dim, L.heads, proj, ldp, b_off, a_off, (const float *) L.a_log, (const float *) L.dt_bias, bg);
+    CKL();
+    return PIB_OK;
+}
+
+// ---- the recurrences -----------------------------------------------------------------------------------------------------------------
+// grid (segment, head, tile of LS_VT value columns), 16 * LS_VT threads: the 16 lanes of a half-warp share one column of the head's
+// [D][V] matrix, lane `part` keeping rows part, part + 16, ... in registers (columns are independent).  A token's inputs come through
+// shared memory in chunks of LS_CHUNK tokens, the next chunk in flight (cp.async) while this one is walked; the matrix is read from the
+// slot at the segment's start and left there at its end.
+//   MODE 0 (time mixing):  o = sum_d a_d (s_d + u_d k_d v),  s_d <- w_d s_d + k_d v                         row = [a D | k D | w D | v LS_VT]
+//   MODE 1 (delta rule):   e = beta (v - g sum_d s_d k_d),  s_d <- g s_d + k_d e,  o = sum_d s_d a_d          row = [a D | k D | v LS_VT | g, beta]
+//       (o is formed from the sums over the old matrix: o = g sum_d s_d a_d + e sum_d k_d a_d, one round of shuffles for all three)
+#define LS_CHUNK 16
+#define LS_VT    8
+struct ls_args {
+    const float * a; int lda, a_hs;          // query-like rows: a[t * lda + group * a_hs + d]
+    const float * k; int ldk, k_hs;
+    const float * w; int ldw;                // MODE 0: decay rows w[t * ldw + h * D + d];   MODE 1: bg rows [beta (H) | g (H)], ldw = 2 H
+    const float * v; int ldv;                // v[t * ldv + h * V + j]
+    const float * u;                         // MODE 0: bonus [H][D]
+    int H, G, D, V;
+    const int32_t * seg_start, * seg_len, * seg_slot;
+    float * state; size_t state_stride, state_off;
+    float * out;                             // [T][H][V]
+};
+template <int RPT, int MODE>
+__global__ void __launch_bounds__(16 * LS_VT) lin_scan_kernel(ls_args A) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
+    extern __shared__ float hs[];
+    const int sg = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * LS_VT, part = threadIdx.x & 15, vl = threadIdx.x >> 4, vd = v0 + vl;
+    const int D = A.D, V = A.V, H = A.H, grp = h / (H / A.G);
+    const int s0 = A.seg_start[sg], n = A.seg_len[sg];
+    const int row_f = (MODE == 0 ? 3 * D : 2 * D) + LS_VT + (MODE == 0 ? 0 : 2);
+    const bool vok = vd < V;
+    float * S = A.state + (size_t) A.seg_slot[sg] * A.state_stride + A.state_off + (size_t) h * D * V;
+    float s[RPT], ub[RPT];
+#pragma unroll
+    for (int r = 0; r < RPT; r++) {
+        const int d = part + 16 * r;
+        s[r] = (d < D && vok) ? S[(size_t) d * V + vd] : 0.f;
+        ub[r] = (MODE == 0 && d < D) ? A.u[(size_t) h * D + d] : 0.f;
+    }
+    auto fetch = [&](int c0, int buf) {
+        const int nc = min(LS_CHUNK, n - c0);
+        for (int t = 0; t < nc; t++) {
+            const size_t tt = (size_t) (s0 + c0 + t);
+            const float * ar = A.a + tt * A.lda + (size_t) grp * A.a_hs;
+            const float * kr = A.k + tt * A.ldk + (size_t) grp * A.k_hs;
+            const uint32_t dst = (uint32_t) __cvta_generic_to_shared(hs + (size_t) (buf * LS_CHUNK + t) * row_f);
+            for (int e = threadIdx.x; e < D; e += blockDim.x) {
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + 4u * e), "l"(ar + e) : "memory");
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + 4u * (D + e)), "l"(kr + e) : "memory");
+                if (MODE == 0) asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + 4u * (2 * D + e)), "l"(A.w + tt * A.ldw + (size_t) h * D + e) : "memory");
+            }
+            const int vbase = MODE == 0 ? 3 * D : 2 * D;
+            if (threadIdx.x < LS_VT && v0 + (int) threadIdx.x < V)
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + 4u * (vbase + threadIdx.x)), "l"(A.v + tt * A.ldv + (size_t) h * V + v0 + threadIdx.x) : "memory");
+            if (MODE == 1 && threadIdx.x >= 32 && threadIdx.x < 34) {       // g, then beta
+                const int which = threadIdx.x - 32;
+                asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + 4u * (vbase + LS_VT + which)), "l"(A.w + tt * A.ldw + (which == 0 ? H : 0) + h) : "memory");
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    if (n > 0) fetch(0, 0);
+    int buf = 0;
+    float * op = A.out + (size_t) s0 * H * V + (size_t) h * V + vd;
+    const int ostride = H * V;
+    for (int c0 = 0; c0 < n; c0 += LS_CHUNK, buf ^= 1) {
+        const int nc = min(LS_CHUNK, n - c0);
+        if (c0 + LS_CHUNK < n) { fetch(c0 + LS_CHUNK, buf ^ 1); asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+        else                   asm volatile("cp.async.wait_group 0;" ::: "memory");
+        __syncthreads();
+        const float * qp = hs + (size_t) buf * LS_CHUNK * row_f;
+        for (int t = 0; t < nc; t++, qp += row_f, op += ostride) {
+            if (MODE == 0) {
+                const float v = vok ? qp[3 * D + vl] : 0.f;
+                float acc = 0.f;
+#pragma unroll
+                for (int r = 0; r < RPT; r++) {
+                    const int d = part + 16 * r;
+                    if (d < D) {
+                        const float kv = qp[D + d] * v;
+                        acc = fmaf(qp[d], fmaf(ub[r], kv, s[r]), acc);
+                        s[r] = fmaf(qp[2 * D + d], s[r], kv);
+                    }
+                }
+                acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+                acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+                acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+                acc += __shfl_xor_sync(0xffffffffu, acc, 8);
+                if (part == 0 && vok) *op = acc;
+            } else {
+                const float v = vok ? qp[2 * D + vl] : 0.f, g = qp[2 * D + LS_VT], beta = qp[2 * D + LS_VT + 1];
+                float sk = 0.f, sa = 0.f, ka = 0.f;
+#pragma unroll
+                for (int r = 0; r < RPT; r++) {
+                    const int d = part + 16 * r;
+                    if (d < D) { const float kd = qp[D + d], ad = qp[d]; sk = fmaf(s[r], kd, sk); sa = fmaf(s[r], ad, sa); ka = fmaf(kd, ad, ka); }
+                }
+#pragma unroll
+                for (int o = 1; o < 16; o <<= 1) {
+                    sk += __shfl_xor_sync(0xffffffffu, sk, o);
+                    sa += __shfl_xor_sync(0xffffffffu, sa, o);
+                    ka += __shfl_xor_sync(0xffffffffu, ka, o);
+                }
+                const float e = beta * (v - g * sk);
+#pragma unroll
+                for (int r = 0; r < RPT; r++) {
+                    const int d = part + 16 * r;
+                    if (d < D) s[r] = fmaf(qp[D + d], e, g * s[r]);
+                }
+                if (part == 0 && vok) *op = fmaf(e, ka, g * sa);
+            }
+        }
+        __syncthreads();                           // everyone is done with this buffer before the fetch after next refills it
+    }
+#pragma unroll
+    for (int r = 0; r < RPT; r++) { const int d = part + 16 * r; if (d < D && vok) S[(size_t) d * V + vd] = s[r]; }
+}
+
+static int lin_scan(int mode, const ls_args & A, int S, cudaStream_t st) {
+    if (A.D > 256) { pib_set_error("recurrence: dim %d not supported (up to 256)", A.D); return PIB_ERR_UNSUPP; }
+    dim3 grid((unsigned) S, (unsigned) A.H, (unsigned) ((A.V + LS_VT - 1) / LS_VT));
+    const size_t smem = (size_t) 2 * LS_CHUNK * ((mode == 0 ? 3 * A.D : 2 * A.D) + LS_VT + (mode == 0 ? 0 : 2)) * 4;
+#define LS_GO(RPT, MODE) do { if (smem > 48 * 1024) cudaFuncSetAttribute(lin_scan_kernel<RPT, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem); \
+                              pib_launch(lin_scan_kernel<RPT, MODE>, dim3(grid), dim3(16 * LS_VT), (size_t) smem, st, A); } while (0)
+#define LS_PICK(MODE) do { if (A.D <= 32) LS_GO(2, MODE); else if (A.D <= 64) LS_GO(4, MODE); else if (A.D <= 128) LS_GO(8, MODE); else LS_GO(16, MODE); } while (0)
+    if (mode == 0) LS_PICK(0); else LS_PICK(1);
+#undef LS_PICK
+#undef LS_GO
+    CKL();
+    return PIB_OK;
+}
+
+// rkvg[t] = [r | k | v | g] (H*D each), wdec[t] = decays (H*D)
+int pib_wkv_scan(const float * rkvg, int ld, const float * wdec, int ldw, const pib_hlayer & L, const pib_hbatch & b, float * state, size_t state_stride, float * out, cudaStream_t st) {
+    const int HD = L.heads * L.dim;
+    ls_args A;
+    A.a = rkvg; A.lda = ld; A.a_hs = L.dim; A.k = rkvg + HD; A.ldk = ld; A.k_hs = L.dim; A.w = wdec; A.ldw = ldw; A.v = rkvg + 2 * HD; A.ldv = ld; A.u = L.bonus;
+    A.H = L.heads; A.G = L.heads; A.D = L.dim; A.V = L.dim; A.seg_start = b.seg_start; A.seg_len = b.seg_len; A.seg_slot = b.seg_slot;
+    A.state = state; A.state_stride = state_stride; A.state_off = L.state_off; A.out = out;
+    return lin_scan(0, A, b.S, st);
+}
+// cv[t] = [q (G*D) | k (G*D) | v (H*V)] prepared by pib_delta_prep, bg[t] = [beta (H) | g (H)]
+int pib_delta_scan(const float * cv, int ldc, const float * bg, const pib_hlayer & L, const pib_hbatch & b, float * state, size_t state_stride, float * out, cudaStream_t st) {
+    const int GD = L.kv_heads * L.dim;
+    ls_args A;
+    A.a = cv; A.lda = ldc; A.a_hs = L.dim; A.k = cv + GD; A.ldk = ldc; A.k_hs = L.dim; A.w = bg; A.ldw = 2 * L.heads; A.v = cv + 2 * GD; A.ldv = ldc; A.u = nullptr;
+    A.H = L.heads; A.G = L.kv_heads; A.D = L.dim; A.V = L.vdim; A.seg_start = b.seg_start; A.seg_len = b.seg_len; A.seg_slot = b.seg_slot;
+    A.state = state; A.state_stride = state_stride; A.state_off = L.state_off; A.out = out;
+    return lin_scan(1, A, b.S, st);
+}
+
+// one warp per (token, head): o <- o / sqrt(mean(o^2) + eps) * w[(h * w_hs) + i] * silu(gate[t * ldg + h * V + i])
+__global__ void gated_head_norm_kernel(float * __restrict__ o, int n_rows, int H, int V, const float * __restrict__ w, int w_hs, const float * __restrict__ gate, int ldg, float eps) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= n_rows) return;
+    const int t = row / H, h = row % H;
+    float * r = o + (size_t) row * V;
+    const float * g = gate + (size_t) t * ldg + (size_t) h * V;
+    const float * wr = w + (size_t) h * w_hs;
+    float s = 0.f;
+    for (int i = lane; i < V; i += 32) s = fmaf(r[i], r[i], s);
+    const float inv = 1.0f / sqrtf(warp_sum(s) / V + eps);
+    for (int i = lane; i < V; i += 32) r[i] = r[i] * inv * wr[i] * mk_silu(g[i]);
+}
+int pib_gated_head_norm(float * o, int T, int H, int V, const float * w, int w_hs, const float * gate, int ldg, float eps, cudaStream_t st) {
+    const int n_rows = T * H;
+    pib_launch(gated_head_norm_kernel, dim3((n_rows + 7) / 8), dim3(256), (size_t) 0, st, o, n_rows, H, V, w, w_hs, gate, ldg, eps);
+    CKL();
+    return PIB_OK;
+}
+
+// ---- clamped gated experts ---------------------------------------------------------------------------------------------------------
+// rows [n_rows][ld] = [gate (F) | up (F)] of an expert's input h; with a weight per row the expert sees w h, and since both products are
+// linear in h the weight multiplies them here.  a = min(w gate, limit), b = clamp(w up, -limit, limit); the row's first F entries become
+// a sigmoid(1.702 a) (b + 1).  scale_of: row -> index into scale (null: the row itself).
+__global__ void glu_clamp_kernel(float * __restrict__ gu, int ld, int F, float limit, const float * __restrict__ scale, const int32_t * __restrict__ scale_of, int n_rows) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
+    const int64_t i = (int64_t) blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (int64_t) n_rows * F) return;
+    const int row = (int) (i / F), c = (int) (i % F);
+    float * r = gu + (size_t) row * ld;
+    const float w = scale ? scale[scale_of ? scale_of[row] : row] : 1.0f;
+    const float a = fminf(w * r[c], limit), b = fminf(fmaxf(w * r[F + c], -limit), limit);
+    r[c] = a * mk_sigmoid(1.702f * a) * (b + 1.0f);
+}
+int pib_glu_clamp(float * gu, int ld, int F, float limit, const float * scale, const int32_t * scale_of, int n_rows, cudaStream_t st) {
+    const int64_t tot = (int64_t) n_rows * F;
+    if (tot <= 0) return PIB_OK;
+    pib_launch(glu_clamp_kernel, dim3((unsigned) ((tot + 255) / 256)), dim3(256), (size_t) 0, st, gu, ld, F, limit, scale, scale_of, n_rows);
+    CKL();
+    return PIB_OK;
+}
+
+// ---- the parallel layer's sum ---------------------------------------------------------------------------------------------------------
+// x[t] += mixer[t] + shared[t] * sigmoid(sgl[t * ldsg]) + sum_k edn[inv[t * top + k]]   (each part optional; k ascending)
+__global__ void parallel_sum_kernel(float * __restrict__ x, const float * __restrict__ mixer, const float * __restrict__ shared, const float * __restrict__ sgl, int ldsg,
+                                    const float * __restrict__ edn, const int32_t * __restrict__ inv, int top, int W) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
+    const int t = blockIdx.x;
+    const float sg = shared ? (sgl ? mk_sigmoid(sgl[(size_t) t * ldsg]) : 1.0f) : 0.f;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        float acc = mixer ? mixer[(size_t) t * W + c] : 0.f;
+        if (shared) acc = fmaf(shared[(size_t) t * W + c], sg, acc);
+        if (edn) for (int k = 0; k < top; k++) acc += edn[(size_t) inv[(size_t) t * top + k] * W + c];
+        x[(size_t) t * W + c] += acc;
+    }
+}
+int pib_parallel_sum(float * x, const float * mixer, const float * shared, const float * sgl, int ldsg, const float * edn, const int32_t * inv, int top, int T, int W, cudaStream_t st) {
+    pib_launch(parallel_sum_kernel, dim3(T), dim3(256), (size_t) 0, st, x, mixer, shared, sgl, ldsg, edn, inv, top, W);
+    CKL();
+    return PIB_OK;
+}

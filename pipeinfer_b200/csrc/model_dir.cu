@@ -150,6 +150,17 @@ struct TensorSource {
     SafeTensors * st = nullptr;
     uint64_t      seed = 0;
     bool          failed = false;
+    bool          norms_around_zero = false;       // synthetic weights: layer norms are stored as w with (1 + w) applied
+    // extent `axis` of a tensor in the file (negative: from the end); `dflt` for a synthetic source or a missing tensor
+    int64_t dim(const std::string & name, int axis, int64_t dflt) const {
+        if (!st) return dflt;
+        auto it = st->t.find(name);
+        if (it == st->t.end()) return dflt;
+        const int n = (int) it->second.shape.size();
+        if (axis < 0) axis += n;
+        return axis >= 0 && axis < n ? it->second.shape[(size_t) axis] : dflt;
+    }
+    bool has(const std::string & name) const { return !st || st->t.count(name) != 0; }
     // the tensor as float32, shape checked
     bool get(const std::string & name, std::initializer_list<int64_t> shape, std::vector<float> & out) {
         int64_t n = 1;
@@ -171,13 +182,19 @@ struct TensorSource {
         uint64_t h = seed * 0x9E3779B97F4A7C15ull + 0x1234567;
         for (char ch : name) h = (h ^ (uint8_t) ch) * 0x100000001B3ull;
         auto next = [&]() { h ^= h << 13; h ^= h >> 7; h ^= h << 17; return (float) ((h >> 11) & 0xFFFFFF) / 16777216.0f; };     // [0, 1)
-        const int64_t last = *(shape.end() - 1);
+        const int64_t last = shape.size() ? *(shape.end() - 1) : 1;
         const bool norm = ends(name, "norm") || ends(name, "norm1") || ends(name, "norm2");
+        const bool around_zero = norms_around_zero && (ends(name, "norm1") || ends(name, "norm2") || name == "final.norm");
         const float amp = 1.5f * sqrtf(3.0f / (float) last);
         for (size_t i = 0; i < out.size(); i++) {
             const float u = next() * 2.f - 1.f;
             float v;
-            if (norm) v = 1.0f + 0.2f * u;
+            if (around_zero) v = 0.2f * u;
+            else if (norm) v = 1.0f + 0.2f * u;
+            else if (name.find(".mu.") != std::string::npos) v = 0.5f + 0.5f * u;
+            else if (ends(name, "vmix")) v = 0.3f;
+            else if (ends(name, ".conv")) v = 0.5f * u + ((int64_t) (i % (size_t) last) == last - 1 ? 0.5f : 0.f);
+            else if (ends(name, "w0") || ends(name, "A_log") || ends(name, "dt_bias") || ends(name, "mix.u")) v = u;
             else if (ends(name, "lower")) v = 0.45f + 0.45f * u;
             else if (ends(name, ".act")) v = (i == 0 ? 0.6f : i == 1 ? 0.3f : i == 2 ? 0.2f : 0.05f);
             else if (ends(name, "sink") || ends(name, "f.b")) v = u;
@@ -217,7 +234,8 @@ static double jnum(const Json * o, const char * k, double dflt, bool * ok = null
 }
 
 // ---- the Rapisun builder ----------------------------------------------------------------------------------------------------------
-// Reads every size and constant from the configuration; tensor names are '<layer>.mix.*', '<layer>.mlp.*', '<layer>.norm1|norm2|canon1'.
+// Sequential layers with LayerNorm on the sublayers' outputs, a causal convolution in front of every mixer, latent attention and HGRN2
+// mixers, PolyNorm and relu^2 mixture-of-experts feed-forwards.  Reads every size and constant from the configuration; tensor names are '<layer>.mix.*', '<layer>.mlp.*', '<layer>.norm1|norm2|canon1'.
 static pib_model * build_rapisun(const Json & cfg, TensorSource & src, int dtype) {
     std::unique_ptr<pib_model, void (*)(pib_model *)> mp(new pib_model(), pib_model_free);
     pib_model * m = mp.get();
@@ -350,9 +368,173 @@ static pib_model * build_rapisun(const Json & cfg, TensorSource & src, int dtype
     return mp.release();
 }
 
+// ---- the Fabivik builder ----------------------------------------------------------------------------------------------------------
+// Parallel layers (x += mixer(N1 x) + ff(N2 x), RMS norms with weights stored around zero), mixers "attention" (windowed softmax
+// attention with short convolutions on q / k / v, per-head query / key norms, grouped queries and value mixing), "wkv" (RWKV-style
+// time mixing) and "delta" (gated delta rule), mixtures of clamped gated experts behind a sigmoid router whose weights multiply the
+// experts' inputs, a gated shared expert.  Every size comes from the configuration or a tensor's shape.
+static pib_model * build_fabivik(const Json & cfg, TensorSource & src, int dtype) {
+    std::unique_ptr<pib_model, void (*)(pib_model *)> mp(new pib_model(), pib_model_free);
+    pib_model * m = mp.get();
+    pib_hybrid * hy = new pib_hybrid();
+    m->hy = hy;
+    m->arch = 2; m->name = "Fabivik";
+    src.norms_around_zero = true;
+    bool ok = true;
+    const int W = (int) jnum(&cfg, "width", 0, &ok), V = (int) jnum(&cfg, "vocab", 0, &ok);
+    const Json * layers = cfg.get("layers");
+    if (!ok || W <= 0 || V <= 0 || !layers || layers->kind != Json::ARR) { pib_set_error("model: config.json needs width, vocab and layers"); return nullptr; }
+    hy->dtype = dtype;
+    hy->form = PIB_FORM_PARALLEL;
+    hy->eps = (float) jnum(cfg.get("norm"), "eps", 1e-5);
+    hy->embd_scale = (float) jnum(cfg.get("embedding"), "scale", 1.0);
+    hy->logit_scale = (float) jnum(&cfg, "logit_scale", 1.0);
+    hy->taps = 0;
+    m->n_embd = W; m->n_vocab = V; m->n_layer = (int) layers->arr.size(); m->layer_begin = 0; m->layer_end = m->n_layer;
+    m->wtype = dtype; m->n_ctx_train = 1 << 20; m->n_head = 1; m->n_head_kv = 1; m->tok_bos = -1; m->tok_eos = -1;
+    std::vector<float> v;
+#define GET(name, ...) do { if (!src.get((name), { __VA_ARGS__ }, v)) return nullptr; } while (0)
+#define VEC(dst, name, n) do { GET(name, (int64_t) (n)); if (!((dst) = upload_f32v(v))) return nullptr; } while (0)
+#define MAT(dst, name, N, K) do { GET(name, (int64_t) (N), (int64_t) (K)); if (!((dst) = upload_mat(v, (N), (K), dtype, m))) return nullptr; } while (0)
+#define APPEND(all, name, N, K) do { GET(name, (int64_t) (N), (int64_t) (K)); (all).insert((all).end(), v.begin(), v.end()); } while (0)
+    MAT(m->tok_embd, "embed", V, W);
+    VEC(m->output_norm, "final.norm", W);
+    MAT(m->output, "head", V, W);
+    hy->layers.resize(m->n_layer);
+    size_t state = 0;
+    int first_mix = -1;
+    auto widen = [](int & a, int64_t b) { if (b > a) a = (int) b; };
+    for (int il = 0; il < m->n_layer; il++) {
+        const Json & jl = layers->arr[il];
+        pib_hlayer & L = hy->layers[il];
+        const std::string p = "l" + std::to_string(il) + ".", px = p + "mix.", pm = p + "mlp.";
+        const Json * ty = jl.get("type"), * mx = jl.get("mixer"), * ml = jl.get("mlp");
+        if (!ty || ty->kind != Json::STR || !mx) { pib_set_error("model: layer %d needs type and mixer", il); return nullptr; }
+        VEC(L.norm1, p + "norm1", W);
+        L.heads = (int) jnum(mx, "heads", 0); L.dim = (int) jnum(mx, "dim", 0);
+        L.kv_heads = (int) jnum(mx, "kv_heads", L.heads); L.vdim = (int) jnum(mx, "vdim", L.dim);
+        L.taps = (int) jnum(mx, "conv", 0);
+        if (L.heads <= 0 || L.dim <= 0 || L.vdim <= 0 || L.kv_heads <= 0 || L.heads % L.kv_heads) { pib_set_error("model: layer %d: heads / kv_heads / dim / vdim", il); return nullptr; }
+        const int64_t H = L.heads, G = L.kv_heads, D = L.dim, Vd = L.vdim;
+        if (ty->str == "attention") {
+            L.mixer = PIB_MIXER_SWA;
+            L.scale = (float) jnum(mx, "scale", 1.0 / sqrt((double) D));
+            const Json * mk = mx->get("mask");
+            L.window = mk && !mk->is_null() ? (int) jnum(mk, "size", 0) : 0;
+            if (L.window <= 0) L.window = 1 << 30;                              // no mask: every earlier token is seen
+            const Json * vm = mx->get("v_mix");
+            const bool mixes = vm && ((vm->kind == Json::BOOL && vm->b) || (vm->kind == Json::NUM && vm->num != 0));
+            const int64_t C = H * D + G * D + G * Vd;
+            std::vector<float> all;
+            APPEND(all, px + "q", H * D, W); APPEND(all, px + "k", G * D, W); APPEND(all, px + "v", G * Vd, W);
+            if (!(L.qkv = upload_mat(all, C, W, dtype, m))) return nullptr;
+            if (L.taps > 0) {
+                all.clear();
+                APPEND(all, px + "q.conv", H * D, L.taps); APPEND(all, px + "k.conv", G * D, L.taps); APPEND(all, px + "v.conv", G * Vd, L.taps);
+                if (!(L.conv = upload_f32v(all))) return nullptr;
+                L.tail_off = state; state += (size_t) (L.taps - 1) * C;
+            }
+            VEC(L.q_norm, px + "q.norm", D);
+            VEC(L.k_norm, px + "k.norm", D);
+            if (mixes) {
+                if (first_mix < 0) { first_mix = il; L.v_mix = 1; }
+                else {
+                    const pib_hlayer & F = hy->layers[first_mix];
+                    if ((int64_t) F.kv_heads * F.vdim != G * Vd) { pib_set_error("model: layer %d mixes its values with layer %d's, which have another size", il, first_mix); return nullptr; }
+                    L.v_mix = 2;
+                    GET(px + "vmix");
+                    L.lambda = v[0];
+                }
+                widen(hy->w_vfirst, G * Vd);
+            }
+            MAT(L.wo, px + "o", W, H * Vd);
+            L.cache_id = hy->n_cache++;
+            hy->cache_row.push_back((int) (G * (D + Vd)));
+            widen(hy->w_proj, C); widen(hy->w_conv, C); widen(hy->w_q, H * D); widen(hy->w_att, H * Vd);
+        } else if (ty->str == "wkv") {
+            L.mixer = PIB_MIXER_WKV;
+            L.kv_heads = L.heads; L.vdim = L.dim;
+            const int64_t HD = H * D;
+            L.w_rank = (int) src.dim(px + "w1", 0, (int64_t) jnum(mx, "decay_rank", 64));
+            if (L.w_rank <= 0) { pib_set_error("model: layer %d: rank of the decay's projections", il); return nullptr; }
+            std::vector<float> all;
+            for (const char * s : { "r", "k", "v", "g", "w" }) { GET(px + "mu." + s, W); all.insert(all.end(), v.begin(), v.end()); }
+            if (!(L.mu = upload_f32v(all))) return nullptr;
+            all.clear();
+            for (const char * s : { "r", "k", "v", "g" }) APPEND(all, px + s, HD, W);
+            if (!(L.rkvg = upload_mat(all, 4 * HD, W, dtype, m))) return nullptr;
+            MAT(L.w1, px + "w1", L.w_rank, W);
+            MAT(L.w2, px + "w2", HD, L.w_rank);
+            VEC(L.w0, px + "w0", HD);
+            GET(px + "u", H, D);
+            if (!(L.bonus = upload_f32v(v))) return nullptr;
+            VEC(L.onorm, px + "norm", HD);
+            MAT(L.wo, px + "o", W, HD);
+            L.shift_off = state; state += (size_t) W;
+            L.state_off = state; state += (size_t) (HD * D);
+            widen(hy->w_shift, 5 * (int64_t) W); widen(hy->w_proj, 4 * HD); widen(hy->w_cq, L.w_rank); widen(hy->w_lat, HD); widen(hy->w_att, HD);
+        } else if (ty->str == "delta") {
+            L.mixer = PIB_MIXER_DELTA;
+            const int64_t C = 2 * G * D + H * Vd, N = C + H * Vd + 2 * H;
+            std::vector<float> all;
+            APPEND(all, px + "q", G * D, W); APPEND(all, px + "k", G * D, W); APPEND(all, px + "v", H * Vd, W); APPEND(all, px + "g", H * Vd, W);
+            APPEND(all, px + "b", H, W); APPEND(all, px + "a", H, W);
+            if (!(L.qkv = upload_mat(all, N, W, dtype, m))) return nullptr;
+            if (L.taps <= 0) L.taps = 1;
+            all.clear();
+            APPEND(all, px + "q.conv", G * D, L.taps); APPEND(all, px + "k.conv", G * D, L.taps); APPEND(all, px + "v.conv", H * Vd, L.taps);
+            if (!(L.conv = upload_f32v(all))) return nullptr;
+            L.tail_off = state; state += (size_t) (L.taps - 1) * C;
+            VEC(L.a_log, px + "A_log", H);
+            VEC(L.dt_bias, px + "dt_bias", H);
+            VEC(L.onorm, px + "norm", Vd);
+            MAT(L.wo, px + "o", W, H * Vd);
+            L.state_off = state; state += (size_t) (H * D * Vd);
+            widen(hy->w_proj, N); widen(hy->w_conv, C); widen(hy->w_cq, 2 * H); widen(hy->w_att, H * Vd);
+        } else { pib_set_error("model: layer %d: unknown mixer '%s'", il, ty->str.c_str()); return nullptr; }
+        if (ml && !ml->is_null()) {
+            VEC(L.norm2, p + "norm2", W);
+            const Json * kind = ml->get("kind");
+            if (!kind || kind->str != "moe") { pib_set_error("model: layer %d: unknown mlp kind", il); return nullptr; }
+            L.mlp = PIB_MLP_MOE; L.route = PIB_ROUTE_SIGMOID; L.expert = PIB_EXPERT_GLU_CLAMP;
+            L.n_experts = (int) jnum(ml->get("router"), "experts", 0); L.top = (int) jnum(ml->get("router"), "top", 0);
+            L.ff_e = (int) jnum(ml->get("expert"), "ff", 0); L.limit_e = (float) jnum(ml->get("expert"), "limit", INFINITY);
+            const Json * sh = ml->get("shared");
+            L.ff_s = sh && !sh->is_null() ? (int) jnum(sh, "ff", 0) : 0;
+            L.limit_s = L.ff_s > 0 ? (float) jnum(sh, "limit", INFINITY) : 0.f;
+            if (L.n_experts <= 0 || L.top <= 0 || L.top > L.n_experts || L.ff_e <= 0) { pib_set_error("model: layer %d: router.experts / router.top / expert.ff", il); return nullptr; }
+            std::vector<float> ups, downs;
+            for (int e = 0; e < L.n_experts; e++) {
+                const std::string pe = pm + "e" + std::to_string(e) + ".";
+                APPEND(ups, pe + "gate", L.ff_e, W); APPEND(ups, pe + "up", L.ff_e, W);
+                APPEND(downs, pe + "down", W, L.ff_e);
+            }
+            if (!(L.e_up = upload_mat(ups, (int64_t) L.n_experts * 2 * L.ff_e, W, dtype, m)) || !(L.e_down = upload_mat(downs, (int64_t) L.n_experts * W, L.ff_e, dtype, m))) return nullptr;
+            GET(pm + "router", L.n_experts, W);
+            if (!(L.router = upload_mat(v, L.n_experts, W, PIB_TYPE_F32, m))) return nullptr;          // the router is always 32-bit
+            if (L.ff_s > 0) {
+                ups.clear();
+                APPEND(ups, pm + "shared.gate", L.ff_s, W); APPEND(ups, pm + "shared.up", L.ff_s, W);
+                L.s_gate = src.has(pm + "shared.sg") ? 1 : 0;
+                if (L.s_gate) APPEND(ups, pm + "shared.sg", 1, W);
+                if (!(L.s_up = upload_mat(ups, 2 * (int64_t) L.ff_s + L.s_gate, W, dtype, m))) return nullptr;
+                MAT(L.s_down, pm + "shared.down", W, L.ff_s);
+                widen(hy->w_proj, 2 * (int64_t) L.ff_s + 8);
+            }
+            widen(hy->w_pairs, L.top); widen(hy->w_eup, (int64_t) L.top * 2 * L.ff_e); widen(hy->w_router, L.n_experts);
+        }
+    }
+    hy->state_floats = state ? state : 4;
+#undef GET
+#undef VEC
+#undef MAT
+#undef APPEND
+    return mp.release();
+}
+
 // ---- registry: config.json "architecture" -> builder ---------------------------------------------------------------------------------
 struct DirArch { const char * name; pib_model * (*build)(const Json &, TensorSource &, int); };
-static const DirArch DIR_ARCHS[] = { { "Rapisun", build_rapisun } };
+static const DirArch DIR_ARCHS[] = { { "Rapisun", build_rapisun }, { "Fabivik", build_fabivik } };
 
 static pib_model * build_from_config(const Json & cfg, TensorSource & src, int dtype) {
     const Json * a = cfg.get("architecture");
@@ -387,8 +569,9 @@ void pib_hybrid_model_free(pib_model * m) {
     pib_hybrid * hy = m->hy;
     if (!hy) return;
     for (pib_hlayer & L : hy->layers) {
-        for (float * f : { L.norm1, L.norm2, L.canon, L.dq_norm, L.dkv_norm, L.sink, L.f_bias, L.lower, L.onorm }) if (f) cudaFree(f);
-        for (pib_weight * w : { L.dqkv, L.uq, L.ukT, L.uv, L.wo, L.qfv, L.up, L.down, L.e_up, L.e_down, L.router, L.s_up, L.s_down }) if (w) pib_weight_free(w);
+        for (float * f : { L.norm1, L.norm2, L.canon, L.dq_norm, L.dkv_norm, L.sink, L.f_bias, L.lower, L.onorm, L.conv, L.q_norm, L.k_norm, L.mu, L.w0, L.bonus, L.a_log,
+                           L.dt_bias }) if (f) cudaFree(f);
+        for (pib_weight * w : { L.dqkv, L.uq, L.ukT, L.uv, L.wo, L.qfv, L.up, L.down, L.e_up, L.e_down, L.router, L.s_up, L.s_down, L.qkv, L.rkvg, L.w1, L.w2 }) if (w) pib_weight_free(w);
     }
     if (hy->embd_norm) cudaFree(hy->embd_norm);
     delete hy;
