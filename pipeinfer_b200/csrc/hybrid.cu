@@ -301,7 +301,7 @@ static int run_layers(pib_context * c, pib_run & run, const pib_hbatch & B, cons
             for (int o = 0; o < g.len; o += per) {
                 const int nq = std::min(per, g.len - o), p0 = B_pos_host[g.start + o];
                 const int j0 = std::max(0, p0 - L.window + 1), NK = p0 + nq - j0;
-                if ((rc = grow_attn_mm(c, (size_t) G * std::max(D, V), 0, nq * H, nq * H, NK)) != PIB_OK) return rc;
+                if ((rc = grow_attn_mm(c, (size_t) G * std::max(D, V), (size_t) 3 * G * D + V, nq * H, nq * H, NK)) != PIB_OK) return rc;
                 RC(HK_KVATTN_MM, 2.0 * nq * H * (double) NK * (D + 2.0 * V), 2.0 * NK * G * (D + 2.0 * V) + 8.0 * nq * H * (D + V) + 8.0 * nq * H * (double) NK,
                    pib_kv_attention_mm(x->q, L, B, cache, row, x->cellmap + (size_t) g.slot * c->n_ctx, g.start + o, nq, j0, NK, x->am_kb, x->am_vt, x->am_q, x->am_s, x->am_p,
                                        x->att, st));

@@ -194,45 +194,60 @@ int pib_kv_attention(const float * q, const pib_hlayer & L, const pib_hbatch & b
 // ---- the same attention as matmuls (long portions, served mode) -----------------------------------------------------------------------
 // For a block of nq consecutive tokens of one segment and the keys [j0, j0 + NK) it can see, one problem per key / value head g:
 // scores [nq * rep][NK] = (scale * queries of the rep heads that share g) x keys^T, the masked softmax over each row, outputs = weights x
-// values.  These kernels prepare the operands -- keys as bfloat16 [G][NKp][D], values transposed and twice side by side [G][V][2 NKp]
-// (a weight enters the value matmul as its bfloat16 part plus the remainder of that rounding), query rows [G][nq * rep][D] -- and put the
-// outputs [G][nq * rep][V] back in token order.
+// values.  Scores keep fp32 accuracy on bfloat16 tensor cores: a number enters as its bfloat16 part and the remainder of that rounding,
+// queries as rows [hi | lo | hi], keys as rows [hi | hi | lo] (3 D wide: hi.hi + lo.hi + hi.lo), and a weight enters the value matmul as
+// [hi | lo] against the values twice side by side.  These kernels prepare the operands -- keys [G][NKp][3 D], values transposed
+// [G][V][2 NKp], query rows [G][nq * rep][3 D], all bfloat16 -- and put the outputs [G][nq * rep][V] back in token order.
+__device__ __forceinline__ void mk_split(float x, __nv_bfloat16 & hi, __nv_bfloat16 & lo) { hi = __float2bfloat16_rn(x); lo = __float2bfloat16_rn(x - __bfloat162float(hi)); }
 __global__ void __launch_bounds__(128) kv_gather_kernel(const float * __restrict__ cache, int cache_row, const int32_t * __restrict__ map, int j0, int NK, int NKp, int G, int D,
                                                         int V, __nv_bfloat16 * __restrict__ Kb, __nv_bfloat16 * __restrict__ Vt) {
     pib_pdl_wait();
     pib_pdl_trigger();
     const int j = blockIdx.x;
-    if (j < NK) {
-        const float * row = cache + (size_t) map[j0 + j] * cache_row;
-        for (int i = threadIdx.x; i < G * D; i += blockDim.x) Kb[((size_t) (i / D) * NKp + j) * D + i % D] = __float2bfloat16_rn(row[i]);
-        for (int i = threadIdx.x; i < G * V; i += blockDim.x) {
-            const __nv_bfloat16 v = __float2bfloat16_rn(row[(size_t) G * D + i]);
-            Vt[(size_t) i * 2 * NKp + j] = v; Vt[(size_t) i * 2 * NKp + NKp + j] = v;
-        }
-    } else {
-        for (int i = threadIdx.x; i < G * D; i += blockDim.x) Kb[((size_t) (i / D) * NKp + j) * D + i % D] = __float2bfloat16_rn(0.f);
-        for (int i = threadIdx.x; i < G * V; i += blockDim.x) { Vt[(size_t) i * 2 * NKp + j] = __float2bfloat16_rn(0.f); Vt[(size_t) i * 2 * NKp + NKp + j] = __float2bfloat16_rn(0.f); }
+    const float * row = j < NK ? cache + (size_t) map[j0 + j] * cache_row : nullptr;
+    for (int i = threadIdx.x; i < G * D; i += blockDim.x) {
+        __nv_bfloat16 hi, lo;
+        mk_split(row ? row[i] : 0.f, hi, lo);
+        __nv_bfloat16 * k = Kb + ((size_t) (i / D) * NKp + j) * 3 * D + i % D;
+        k[0] = hi; k[D] = hi; k[2 * D] = lo;
+    }
+    for (int i = threadIdx.x; i < G * V; i += blockDim.x) {
+        const __nv_bfloat16 v = __float2bfloat16_rn(row ? row[(size_t) G * D + i] : 0.f);
+        Vt[(size_t) i * 2 * NKp + j] = v; Vt[(size_t) i * 2 * NKp + NKp + j] = v;
     }
 }
-// dir 0: Qc[g][ti * rep + hr][D] = scale * q[t0 + ti][g * rep + hr][D];   dir 1: out[t0 + ti][g * rep + hr][V] = O[g][ti * rep + hr][V]
-__global__ void __launch_bounds__(128) kv_regroup_kernel(const float * __restrict__ src, float * __restrict__ dst, int H, int rep, int nq, int n, int t0, float scale, int dir) {
+// Qc[g][ti * rep + hr] = [hi | lo | hi] of scale * q[t0 + ti][g * rep + hr]
+__global__ void __launch_bounds__(128) kv_query_rows_kernel(const float * __restrict__ q, __nv_bfloat16 * __restrict__ Qc, int H, int rep, int nq, int D, int t0, float scale) {
     pib_pdl_wait();
     pib_pdl_trigger();
     const int ti = blockIdx.x, h = blockIdx.y, g = h / rep, hr = h % rep;
-    const size_t tok = ((size_t) (t0 + ti) * H + h) * n, grp = ((size_t) g * nq * rep + (size_t) ti * rep + hr) * n;
-    if (dir == 0) for (int i = threadIdx.x; i < n; i += blockDim.x) dst[grp + i] = src[tok + i] * scale;
-    else          for (int i = threadIdx.x; i < n; i += blockDim.x) dst[tok + i] = src[grp + i];
+    const float * src = q + ((size_t) (t0 + ti) * H + h) * D;
+    __nv_bfloat16 * dst = Qc + ((size_t) g * nq * rep + (size_t) ti * rep + hr) * 3 * D;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        __nv_bfloat16 hi, lo;
+        mk_split(src[i] * scale, hi, lo);
+        dst[i] = hi; dst[D + i] = lo; dst[2 * D + i] = hi;
+    }
+}
+// out[t0 + ti][g * rep + hr][V] = O[g][ti * rep + hr][V]
+__global__ void __launch_bounds__(128) kv_token_order_kernel(const float * __restrict__ O, float * __restrict__ out, int H, int rep, int nq, int V, int t0) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
+    const int ti = blockIdx.x, h = blockIdx.y, g = h / rep, hr = h % rep;
+    const float * src = O + ((size_t) g * nq * rep + (size_t) ti * rep + hr) * V;
+    float * dst = out + ((size_t) (t0 + ti) * H + h) * V;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) dst[i] = src[i];
 }
 int pib_kv_attention_mm(const float * q, const pib_hlayer & L, const pib_hbatch & b, const float * cache, int cache_row, const int32_t * map, int t0, int nq, int j0, int NK,
                         void * Kb, void * Vt, float * Qc, float * S, void * P, float * out, cudaStream_t st) {
     const int H = L.heads, G = L.kv_heads, D = L.dim, V = L.vdim, rep = H / G, NKp = (NK + 7) & ~7, M = nq * rep;
     pib_launch(kv_gather_kernel, dim3(NKp), dim3(128), (size_t) 0, st, cache, cache_row, map, j0, NK, NKp, G, D, V, (__nv_bfloat16 *) Kb, (__nv_bfloat16 *) Vt);
     CKL();
-    pib_launch(kv_regroup_kernel, dim3((unsigned) nq, (unsigned) H), dim3(128), (size_t) 0, st, q, Qc, H, rep, nq, D, t0, L.scale, 0);
+    pib_launch(kv_query_rows_kernel, dim3((unsigned) nq, (unsigned) H), dim3(128), (size_t) 0, st, q, (__nv_bfloat16 *) Qc, H, rep, nq, D, t0, L.scale);
     CKL();
     pib_mm a;
-    a.W = Kb; a.wtype = PIB_TYPE_BF16; a.ldw = D; a.wz = (int64_t) NKp * D; a.X = Qc; a.ldx = D; a.xz = (int64_t) M * D; a.Y = S; a.ldy = NKp; a.yz = (int64_t) M * NKp;
-    a.M = M; a.N = NK; a.K = D; a.Z = G;
+    a.W = Kb; a.wtype = PIB_TYPE_BF16; a.ldw = 3 * D; a.wz = (int64_t) NKp * 3 * D; a.X = Qc; a.ldx = 3 * D; a.xz = (int64_t) M * 3 * D; a.x_bf16 = 1;
+    a.Y = S; a.ldy = NKp; a.yz = (int64_t) M * NKp; a.M = M; a.N = NK; a.K = 3 * D; a.Z = G;
     int rc = pib_dense_mm(a, st);
     if (rc != PIB_OK) return rc;
     if ((rc = pib_window_softmax(S, P, NKp, NK, j0, L.window, b.pos, t0, G * M, M, rep, L.sink, st)) != PIB_OK) return rc;
@@ -240,7 +255,7 @@ int pib_kv_attention_mm(const float * q, const pib_hlayer & L, const pib_hbatch 
     v.W = Vt; v.wtype = PIB_TYPE_BF16; v.ldw = 2 * NKp; v.wz = (int64_t) V * 2 * NKp; v.X = (const float *) P; v.ldx = 2 * NKp; v.xz = (int64_t) M * 2 * NKp; v.x_bf16 = 1;
     v.Y = Qc; v.ldy = V; v.yz = (int64_t) M * V; v.M = M; v.N = V; v.K = 2 * NKp; v.Z = G;               // the query rows are used up: the outputs take their place
     if ((rc = pib_dense_mm(v, st)) != PIB_OK) return rc;
-    pib_launch(kv_regroup_kernel, dim3((unsigned) nq, (unsigned) H), dim3(128), (size_t) 0, st, (const float *) Qc, out, H, rep, nq, V, t0, 1.0f, 1);
+    pib_launch(kv_token_order_kernel, dim3((unsigned) nq, (unsigned) H), dim3(128), (size_t) 0, st, (const float *) Qc, out, H, rep, nq, V, t0);
     CKL();
     return PIB_OK;
 }

@@ -1,7 +1,8 @@
-"""`bench.py --design rapisun`: prefill and decode throughput of the Rapisun design at sizes that resemble a real model's layers
-(random weights drawn in the loader from a seed), beside the closest existing model of the library at equal width / depth / vocabulary
-(llama architecture, Q4_K, whose prompts run on its tcgen05 GEMM and whose decoding on its tensor-core GEMVs), plus the share and
-the roofline fraction of every kind of launch.  Everything goes through llama_decode on host batches; times are medians of CUDA-side
+"""`bench.py --design rapisun | fabivik`: prefill and decode throughput of a layer-list design at sizes that resemble a real model's
+layers (random weights drawn in the loader from a seed), beside the closest existing model of the library at equal width / depth /
+vocabulary -- for Rapisun the llama architecture in Q4_K (prompts on its tcgen05 GEMM, decoding on its tensor-core GEMVs), for Fabivik
+the Rapisun design (the other layer-list model: same runtime, same dense matmuls) -- plus the share and the roofline fraction of every
+kind of launch.  Everything goes through llama_decode on host batches; times are medians of CUDA-side
 work as seen by the caller (llama_decode returns after the run's event), the per-kind numbers come from CUDA events around each
 launch (llama_pib_profile_layer).  One JSON line on stdout."""
 import ctypes as C
@@ -36,6 +37,20 @@ def design_config(width, vocab, blocks, heads, window, ff, experts, top, ff_e, f
                    {"type": "hgrn2", "mixer": h, "mlp": moe},
                    {"type": "hgrn2", "mixer": h, "mlp": dense}]
     return {"architecture": "Rapisun", "width": width, "vocab": vocab, "canon": {"taps": 4}, "norm": {"eps": 1e-5}, "layers": layers}
+
+
+def fabivik_config(width, vocab, blocks, heads, window, experts, top, ff_e, ff_s, **_):
+    """one block = [attention + MoE, delta rule + MoE, attention (values mixed with the first one's) + MoE, time mixing + MoE]"""
+    dim = 128
+    moe = {"kind": "moe", "router": {"experts": experts, "top": top}, "expert": {"ff": ff_e, "limit": 7.0}, "shared": {"ff": ff_s, "limit": 7.0}}
+    att = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": dim, "vdim": dim, "conv": 4, "mask": {"size": window}, "scale": 1.0 / math.sqrt(dim), "v_mix": True}
+    dlt = {"heads": heads, "kv_heads": max(1, heads // 2), "dim": dim, "vdim": dim, "conv": 4}
+    wkv = {"heads": width // 64, "dim": 64, "decay_rank": 64}
+    layers = []
+    for _ in range(blocks):
+        layers += [{"type": "attention", "mixer": att, "mlp": moe}, {"type": "delta", "mixer": dlt, "mlp": moe},
+                   {"type": "attention", "mixer": att, "mlp": moe}, {"type": "wkv", "mixer": wkv, "mlp": moe}]
+    return {"architecture": "Fabivik", "width": width, "vocab": vocab, "norm": {"eps": 1e-5}, "embedding": {"scale": 8.0}, "logit_scale": 0.5, "layers": layers}
 
 
 SIZES = {
@@ -187,26 +202,37 @@ def run(args):
         scratch.zero_()
         torch.cuda.synchronize()
 
-    out = {"design": "Rapisun", "metric": "prefill / decode tokens per second, one GPU", "dtype": "bf16 operands, fp32 accumulation (comparator: Q4_K x Q8_K)",
+    fab = args.design == "fabivik"
+    out = {"design": "Fabivik" if fab else "Rapisun", "metric": "prefill / decode tokens per second, one GPU",
+           "dtype": "bf16 operands, fp32 accumulation" + ("" if fab else " (comparator: Q4_K x Q8_K)"),
+           "comparator": "Rapisun (layer-list design of this library), same width / depth / vocabulary / experts" if fab else "llama architecture, Q4_K",
            "data": "synthetic (random weights from a seed)", "peaks": peaks, "l2_policy": "256 MB written between timed calls", "sizes": {}}
     lens = [int(x) for x in args.design_prompt.split(",")]
     for name in args.design_size.split(","):
         dargs, cmp_shape = SIZES[name]
-        cfg = design_config(**dargs)
+        cfg = fabivik_config(**dargs) if fab else design_config(**dargs)
         vocab = dargs["vocab"]
         n_ctx = max(lens) + 512
+        key = "fabivik" if fab else "rapisun"
         t0 = time.time()
         ours = llama.Context(config=json.dumps(cfg), seed=1, n_ctx=4 * 320 + n_ctx, max_seq=8, state_slots=4)
         entry = {"config": dargs, "layers": len(cfg["layers"]), "load_s": round(time.time() - t0, 1)}
-        entry["rapisun"] = _measure(ours, lib, lens, 32, [1, 4], vocab, flush, args.warmup, args.steps)
-        entry["rapisun_prefill_kinds"] = _profile_design(ours, lib, max(lens), vocab, False, peaks)
-        entry["rapisun_decode_kinds"] = _profile_design(ours, lib, 256, vocab, True, peaks)
+        entry[key] = _measure(ours, lib, lens, 32, [1, 4], vocab, flush, args.warmup, args.steps)
+        entry[key + "_prefill_kinds"] = _profile_design(ours, lib, max(lens), vocab, False, peaks)
+        entry[key + "_decode_kinds"] = _profile_design(ours, lib, 256, vocab, True, peaks)
         ours.close()
-        L, E, H, HKV, FF, V = cmp_shape
-        cmpc = llama.Context(None, n_ctx=4 * 320 + n_ctx, max_seq=8, synthetic=(L, E, H, HKV, FF, V, 12, 1, 1, 1.0))
-        entry["llama_q4k"] = _measure(cmpc, lib, lens, 32, [1, 4], vocab, flush, args.warmup, args.steps)
-        entry["llama_q4k_decode_kinds"] = _profile_llama(cmpc, lib, L // 2, 256, vocab, peaks)
-        cmpc.close()
+        if fab:
+            cmpc = llama.Context(config=json.dumps(design_config(**dargs)), seed=1, n_ctx=4 * 320 + n_ctx, max_seq=8, state_slots=4)
+            entry["rapisun"] = _measure(cmpc, lib, lens, 32, [1, 4], vocab, flush, args.warmup, args.steps)
+            entry["rapisun_prefill_kinds"] = _profile_design(cmpc, lib, max(lens), vocab, False, peaks)
+            entry["rapisun_decode_kinds"] = _profile_design(cmpc, lib, 256, vocab, True, peaks)
+            cmpc.close()
+        else:
+            L, E, H, HKV, FF, V = cmp_shape
+            cmpc = llama.Context(None, n_ctx=4 * 320 + n_ctx, max_seq=8, synthetic=(L, E, H, HKV, FF, V, 12, 1, 1, 1.0))
+            entry["llama_q4k"] = _measure(cmpc, lib, lens, 32, [1, 4], vocab, flush, args.warmup, args.steps)
+            entry["llama_q4k_decode_kinds"] = _profile_llama(cmpc, lib, L // 2, 256, vocab, peaks)
+            cmpc.close()
         out["sizes"][name] = entry
     print(json.dumps(out))
     return 0
