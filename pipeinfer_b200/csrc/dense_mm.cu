@@ -8,8 +8,9 @@
 // strides; with `zrange` problem z owns a run of rows of a sorted list (tokens grouped by expert) and rows may be gathered
 // through an index list.
 //
-// Kernels: mm_tile_kernel (any shape; 64 x 64 x 16 tiles, 4 x 4 outputs per thread) and, for up to MV_MAXB rows, mv_rows_kernel
-// (one warp per weight row, 16-byte weight loads: the weights are read once at the speed of memory).
+// Kernels: mm_tile_kernel (any shape; 64 x 64 x 16 tiles, 4 x 4 outputs per thread), for up to MV_MAXB rows mv_rows_kernel
+// (one warp per weight row, 16-byte weight loads: the weights are read once at the speed of memory), and for up to 32 float32 outputs
+// over many rows mm_few_cols_kernel (a warp per row: a router's logits, where 64-wide output tiles would leave most of the machine idle).
 #include "hybrid.cuh"
 
 #include <cuda_bf16.h>
@@ -124,17 +125,9 @@ template <> struct wvec<float> {
     }
 };
 
+// the rows [row0, row1) of problem z (at most B of them) against weight row n
 template <typename WT, bool ROUND, int EPI, int B>
-__global__ void __launch_bounds__(256) mv_rows_kernel(mm_dev a, bool xvec) {
-    pib_pdl_wait();
-    pib_pdl_trigger();
-    const int z = blockIdx.z;
-    int row0 = 0, row1 = a.M;
-    if (a.zrange) { row0 = a.zrange[z]; row1 = a.zrange[z + 1]; }
-    if (row1 - row0 > B) row1 = row0 + B;            // the host only picks this kernel when every z has at most B rows
-    if (row0 >= row1) return;
-    const int lane = threadIdx.x & 31, n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (n >= a.N) return;
+__device__ __forceinline__ void mv_rows_body(const mm_dev & a, bool xvec, int z, int n, int lane, int row0, int row1) {
     const WT *    W = reinterpret_cast<const WT *>(a.W) + (size_t) z * a.wz + (size_t) n * a.ldw;
     const float * X = a.X + (size_t) z * a.xz;
     float *       Y = a.Y + (size_t) z * a.yz;
@@ -182,6 +175,55 @@ __global__ void __launch_bounds__(256) mv_rows_kernel(mm_dev a, bool xvec) {
     }
 }
 
+// B = the most rows any problem can own (the batch's total).  A grouped problem (zrange) usually owns fewer -- an expert of a decode
+// step has one or two of the batch's pairs -- and takes the instance that fits its own count, so that it stays bound by its weights' bytes
+// and not by B times the arithmetic.  Every row's sum is formed in the same order whichever instance runs.
+template <typename WT, bool ROUND, int EPI, int B>
+__global__ void __launch_bounds__(256) mv_rows_kernel(mm_dev a, bool xvec) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
+    const int z = blockIdx.z;
+    int row0 = 0, row1 = a.M;
+    if (a.zrange) { row0 = a.zrange[z]; row1 = a.zrange[z + 1]; }
+    if (row1 - row0 > B) row1 = row0 + B;            // the host only picks this kernel when every z has at most B rows
+    if (row0 >= row1) return;
+    const int lane = threadIdx.x & 31, n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (n >= a.N) return;
+    const int cnt = row1 - row0;
+    if (B > 1 && a.zrange && cnt < B) {
+        if (cnt == 1)                { mv_rows_body<WT, ROUND, EPI, 1>(a, xvec, z, n, lane, row0, row1); return; }
+        if (B > 2 && cnt <= 2)       { mv_rows_body<WT, ROUND, EPI, 2>(a, xvec, z, n, lane, row0, row1); return; }
+        if (B > 4 && cnt <= 4)       { mv_rows_body<WT, ROUND, EPI, (B > 4 ? 4 : B)>(a, xvec, z, n, lane, row0, row1); return; }
+        if (B > 8 && cnt <= 8)       { mv_rows_body<WT, ROUND, EPI, (B > 8 ? 8 : B)>(a, xvec, z, n, lane, row0, row1); return; }
+    }
+    mv_rows_body<WT, ROUND, EPI, B>(a, xvec, z, n, lane, row0, row1);
+}
+
+// ---- few outputs, many rows (a router's logits over a prompt): one warp per row m, lanes stride over k, NB accumulators per lane ----
+// float32 weights and activations, no rounding; the weight matrix (N x K floats) stays in L1 / L2 while every warp walks it.
+template <int NB>
+__global__ void __launch_bounds__(256) mm_few_cols_kernel(mm_dev a) {
+    pib_pdl_wait();
+    pib_pdl_trigger();
+    const int lane = threadIdx.x & 31, m = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (m >= a.M) return;
+    const float * W = reinterpret_cast<const float *>(a.W);
+    const float * x = a.X + (size_t) m * a.ldx;
+    float acc[NB];
+#pragma unroll
+    for (int n = 0; n < NB; n++) acc[n] = 0.f;
+    for (int k = lane; k < a.K; k += 32) {
+        const float xv = x[k];
+#pragma unroll
+        for (int n = 0; n < NB; n++) if (n < a.N) acc[n] = fmaf(xv, W[(size_t) n * a.ldw + k], acc[n]);
+    }
+#pragma unroll
+    for (int n = 0; n < NB; n++) {
+        const float v = warp_sum(acc[n]);
+        if (lane == 0 && n < a.N) a.Y[(size_t) m * a.ldy + n] = v;
+    }
+}
+
 template <typename WT, bool ROUND, int EPI>
 static int launch_mm(const pib_mm & a, const mm_dev & d, cudaStream_t st) {
     const int  V = wvec<WT>::N;
@@ -215,6 +257,14 @@ int pib_dense_mm(const pib_mm & a, cudaStream_t st) {
     }
     if (a.x_bf16) { pib_set_error("dense matmul: bfloat16 activations need the tensor-core path (more than 16 rows, strides multiples of 8)"); return PIB_ERR_UNSUPP; }
     mm_dev d = { a.W, a.ldw, a.wz, a.X, a.ldx, a.xz, a.xrows, a.xdiv < 1 ? 1 : a.xdiv, a.Y, a.ldy, a.yz, a.M, a.N, a.K, a.zrange };
+    if (a.wtype == PIB_TYPE_F32 && a.exact && a.N <= 32 && a.M > MV_MAXB && a.Z == 1 && !a.xrows && !a.zrange && a.epi == PIB_EPI_NONE) {
+        dim3 grid((unsigned) ((a.M + 7) / 8));
+        if (a.N <= 8)       pib_launch(mm_few_cols_kernel<8>, dim3(grid), dim3(256), (size_t) 0, st, d);
+        else if (a.N <= 16) pib_launch(mm_few_cols_kernel<16>, dim3(grid), dim3(256), (size_t) 0, st, d);
+        else                pib_launch(mm_few_cols_kernel<32>, dim3(grid), dim3(256), (size_t) 0, st, d);
+        PIB_CHECK(cudaGetLastError());
+        return PIB_OK;
+    }
 #define MM_GO(WT, ROUND) (a.epi == PIB_EPI_RELU2 ? launch_mm<WT, ROUND, PIB_EPI_RELU2>(a, d, st) : launch_mm<WT, ROUND, PIB_EPI_NONE>(a, d, st))
     if (a.wtype == PIB_TYPE_BF16) return MM_GO(__nv_bfloat16, true);
     if (a.wtype == PIB_TYPE_F32) return a.exact ? MM_GO(float, false) : MM_GO(float, true);
