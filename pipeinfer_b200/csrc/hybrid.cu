@@ -189,8 +189,10 @@ static int grow_scratch(pib_context * c, int T) {
 }
 
 // ---- the layers -----------------------------------------------------------------------------------------------------------------------
-// Attention of a segment of at least MM_ATTN_MIN_LEN tokens runs as matmuls on the tensor cores (served mode, latent rows of at least
-// MM_ATTN_MIN_ROW floats, a multiple of 8), in blocks of MM_ATTN_BLOCK tokens; everything else stays with latent_attn_kernel.
+// Attention of a segment of at least MM_ATTN_MIN_LEN tokens runs as matmuls on the tensor cores in served mode, in blocks of at most
+// MM_ATTN_BLOCK tokens: latent attention when its rows have at least MM_ATTN_MIN_ROW floats (a multiple of 8), key / value-head
+// attention when the head size is a multiple of 8.  Everything else (decoded tokens, short portions, float32 contexts) stays with the
+// per-token kernels.
 #define MM_ATTN_MIN_LEN 128
 #define MM_ATTN_MIN_ROW 192
 #define MM_ATTN_BLOCK   512

@@ -2,7 +2,7 @@
 // norms, rotations, attention scores and weights, gates and the recurrence, the router.
 //
 //   LayerNorm (weight, no bias) on a sublayer's output, added to the residual stream
-//   causal convolution over time in front of a mixer, its last taps-1 inputs kept per sequence
+//   causal convolution over time on any run of channels (in front of a mixer, or on projected q | k | v), its last taps-1 inputs kept per sequence
 //   latent attention: per token one cached row [c | k_rot]; queries are folded through W_uk ("absorbed"), so a score is
 //       (q_lat . c + q_rot . k_rot) * scale, softmax over a sliding window plus one learned sink logit per head, and the
 //       output is sum_j p_j c_j (folded through W_uv by the caller)

@@ -487,7 +487,10 @@ static int lin_scan(int mode, ls_args & A, int S, cudaStream_t st) {
     if (A.D > 256) { pib_set_error("recurrence: dim %d not supported (up to 256)", A.D); return PIB_ERR_UNSUPP; }
     dim3 grid((unsigned) S, (unsigned) A.H, (unsigned) ((A.V + LS_VT - 1) / LS_VT));
     const size_t row_f = (size_t) (mode == 0 ? 3 * A.D : 2 * A.D) + LS_VT + (mode == 0 ? 0 : 2) + 1;
-    A.chunk = row_f * 4 * 2 * 32 <= 100 * 1024 ? 32 : 16;
+    // chunks of 32 tokens halve the barriers per token, but their double buffer must not push part of the grid into a second wave
+    const size_t smem32 = row_f * 4 * 2 * 32;
+    const size_t per_sm = smem32 <= 100 * 1024 ? (size_t) (227 * 1024) / (smem32 + 1024) : 0;
+    A.chunk = per_sm > 0 && (size_t) grid.x * grid.y * grid.z <= per_sm * (size_t) pib_num_sms() ? 32 : 16;
     const size_t smem = (size_t) 2 * A.chunk * row_f * 4;
 #define LS_GO(RPT, MODE, FULL) do { if (smem > 48 * 1024) cudaFuncSetAttribute(lin_scan_kernel<RPT, MODE, FULL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int) smem); \
                                     pib_launch(lin_scan_kernel<RPT, MODE, FULL>, dim3(grid), dim3(16 * LS_VT), (size_t) smem, st, A); } while (0)
